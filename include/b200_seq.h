@@ -110,6 +110,37 @@ int b200_seq_moe_gather_rows(const void* A, int dt, int64_t lda, void* out, int3
 /* resid += mix + sum_k weights[t, k] y[row(t, k)]; mix and y may be NULL */
 int b200_seq_moe_combine_add(float* resid, const float* mix, const float* y, int64_t ldy, const float* weights, int32_t* plan, int64_t T,
                              int E, int top, int64_t W, void* stream);
+/* mode 0: as b200_seq_moe_route; mode 1: scores = sigmoid(logit), the picks are the largest score + correction[expert] (element type
+ * corr_dt, may be NULL), weights = picked score / (sum of the picked scores + 1e-20) * weight_scale */
+int b200_seq_moe_route_scored(const float* logits, int64_t T, int E, int top, int mode, const void* correction, int corr_dt, float weight_scale,
+                              int32_t* ids, float* weights, int32_t* plan, void* stream);
+/* resid (fp32) += v / sqrt(mean v^2 + eps) * w, v = y * sigmoid(gate) (gate NULL: y); typed (type dt, may be NULL) = the updated rows */
+int b200_seq_gated_rms_add(const float* y, const float* gate, const void* w, int dt, float* resid, void* typed, int64_t T, int64_t W, float eps,
+                           void* stream);
+/* out (type dt) = x, n fp32 values */
+int b200_seq_cast_rows(const float* x, void* out, int dt, int64_t n, void* stream);
+/* rows [g | u] (type dt, 2F wide) -> act(g) * u; act 0: SiLU, 1: GELU in its tanh form */
+int b200_seq_ff_gate(const void* gu, void* out, int dt, int64_t rows, int64_t F, int act, void* stream);
+/* gated delta rule over fp32 state slots S [slots, H, dk, dv]: per token S <- g S, u = beta (v - S^T k), S <- S + k u^T, y = S^T q; q and k
+ * (kv_heads x dk, shared by H / kv_heads heads) are made unit vectors, q times q_scale; beta = sigmoid(raw[col_b + h]),
+ * g = exp(-exp(A_log[h]) softplus(raw[col_a + h] + dt_bias[h])); c holds the activated q / k / v columns; y fp32 [T, H * dv] */
+int b200_seq_delta_scan(const float* c, int64_t ldc, int col_q, int col_k, int col_v, const float* raw, int64_t ldr, int col_b, int col_a,
+                        const void* A_log, const void* dt_bias, int dt, float q_scale, float* S_state, const int32_t* state_slots,
+                        const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int kv_heads, int dk, int dv,
+                        void* stream);
+/* per token: RMS norm over the whole q projection (H * d columns) and the whole k projection (G * d) when whole_norm != 0 (weights per
+ * column, may be NULL), rotation of the first `rot` columns of every head, column i paired with i + rot / 2 (cos / sin fp32
+ * [positions, rot / 2]); keys and values to the token-major cache row [k_off: G * d | v_off: G * dv], queries to q_out fp32 [T, H * d] */
+int b200_seq_qk_rot_prepare(const float* src, int64_t ld, int col_q, int col_k, int col_v, int H, int G, int d, int dv, const void* qnorm_w,
+                            const void* knorm_w, int whole_norm, float eps, const float* cos_t, const float* sin_t, int rot,
+                            const int64_t* position_ids, const int64_t* slot_mapping, void* cache, int dt, int64_t row_width, int k_off,
+                            int v_off, float* q_out, int64_t T, void* stream);
+/* attention with the scaled scores mixed over the heads before the soft-max (talk fp32 [H, H], NULL: none); a query at p sees keys
+ * j <= p with floor(j / chunk) == floor(p / chunk) (chunk > 0) and p - j < window (window > 0); out fp32 [T, H, dv] */
+int b200_seq_talk_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
+                       int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids,
+                       const float* talk, float* out, int64_t T, int H, int G, int d, int dv, int chunk, int window, float scale, int page,
+                       void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,5 +1,7 @@
-// Routed feed-forward (mixture of experts): every token picks the `top` experts with the largest router logits and weighs
-// them by the soft-max over the picked logits only.
+// Routed feed-forward (mixture of experts): every token picks `top` experts and weighs them, by one of two rules:
+//   mode 0  the largest router logits; weights = soft-max over the picked logits only;
+//   mode 1  scores s = sigmoid(logit); the largest s + correction[expert] are picked, the weights are the picked plain scores
+//           divided by their sum (+ 1e-20), times a constant.
 //
 //   moe_route_kernel   : one warp per token: top-k of the fp32 logits (ties: the lower expert), weights, and the token's place in
 //                        each picked expert's list (an atomic counter per expert; the order inside a list changes no result).
@@ -44,18 +46,25 @@ __host__ __device__ inline MoePlan moe_plan_view(int32_t* base, int64_t T, int E
   return p;
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int64_t T, int E, int top, int32_t* __restrict__ ids,
-                                                        float* __restrict__ weights, int32_t* __restrict__ counts, int32_t* __restrict__ place) {
+                                                        float* __restrict__ weights, int32_t* __restrict__ counts, int32_t* __restrict__ place,
+                                                        const void* __restrict__ correction, int corr_dt, float weight_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t t = (int64_t)blockIdx.x * 8 + warp_id();
   if (t >= T) return;
   const int lane = lane_id();
-  float z[kMaxExpertsPerLane];
+  float z[kMaxExpertsPerLane], sc[kMaxExpertsPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxExpertsPerLane; ++i) {
     const int e = lane + 32 * i;
     z[i] = e < E ? logits[t * E + e] : -INFINITY;
+    sc[i] = 0.f;
+    if (MODE == 1 && e < E) {
+      sc[i] = sigmoid_f(z[i]);
+      z[i] = sc[i] + (correction ? ld_any(correction, e, corr_dt) : 0.f);
+    }
   }
   float val[kMaxTop];
   int idx[kMaxTop];
@@ -75,6 +84,13 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
       if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
     }
+    if (MODE == 1) {  // the weight uses the plain score of the pick, which its owning lane holds
+      float mine = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMaxExpertsPerLane; ++i)
+        if (lane + 32 * i == be) mine = sc[i];
+      best = __shfl_sync(0xffffffffu, mine, be & 31);
+    }
     val[k] = best;
     idx[k] = be;
 #pragma unroll
@@ -86,14 +102,15 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
 #pragma unroll
     for (int k = 0; k < kMaxTop; ++k) {
       if (k >= top) break;
-      w[k] = expf(val[k] - val[0]);  // val[0] is the largest
+      w[k] = MODE == 1 ? val[k] : expf(val[k] - val[0]);  // mode 0: val[0] is the largest
       den += w[k];
     }
+    const float norm = MODE == 1 ? weight_scale / (den + 1e-20f) : 1.f / den;
 #pragma unroll
     for (int k = 0; k < kMaxTop; ++k) {
       if (k >= top) break;
       ids[t * top + k] = idx[k];
-      weights[t * top + k] = w[k] / den;
+      weights[t * top + k] = w[k] * norm;
       place[t * top + k] = atomicAdd(counts + idx[k], 1);
     }
   }
@@ -304,7 +321,10 @@ extern "C" int64_t b200_seq_moe_plan_ints(int64_t T, int E, int top) {
 }
 
 // logits fp32 [T, E] -> ids int32 [T, top], weights fp32 [T, top] and the plan (b200_seq_moe_plan_ints int32 values)
-extern "C" int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* ids, float* weights, int32_t* plan, void* stream) {
+// mode 0: soft-max over the picked logits (correction, weight_scale unused); mode 1: sigmoid scores, picks by score + correction
+// (element type corr_dt, may be NULL), weights = score / sum of the picked scores * weight_scale
+extern "C" int b200_seq_moe_route_scored(const float* logits, int64_t T, int E, int top, int mode, const void* correction, int corr_dt,
+                                         float weight_scale, int32_t* ids, float* weights, int32_t* plan, void* stream) {
   if (T == 0) return B200_OK;
   if (E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 || top > kMaxTop || top > E) {
     b200_set_last_error("seq_moe_route: need 1 <= top <= min(16, experts), experts <= 256");
@@ -313,10 +333,19 @@ extern "C" int b200_seq_moe_route(const float* logits, int64_t T, int E, int top
   cudaStream_t st = (cudaStream_t)stream;
   MoePlan p = moe_plan_view(plan, T, E, top);
   if (cudaMemsetAsync(p.counts, 0, sizeof(int32_t) * E, st) != cudaSuccess) { b200_set_last_error("seq_moe_route: memset failed"); return B200_ERR_CUDA; }
-  B200_LAUNCH(moe_route_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, st, logits, T, E, top, ids, weights, p.counts, p.place);
+  if (mode == 1)
+    B200_LAUNCH(moe_route_kernel<1>, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, st, logits, T, E, top, ids, weights, p.counts, p.place, correction,
+                corr_dt, weight_scale);
+  else
+    B200_LAUNCH(moe_route_kernel<0>, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, st, logits, T, E, top, ids, weights, p.counts, p.place, correction,
+                corr_dt, weight_scale);
   B200_LAUNCH(moe_plan_kernel, dim3(1), dim3(256), 0, st, (const int32_t*)ids, T * top, top, E, p);
   b200_count_launches(2);
   return B200_OK;
+}
+
+extern "C" int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* ids, float* weights, int32_t* plan, void* stream) {
+  return b200_seq_moe_route_scored(logits, T, E, top, 0, nullptr, B200_DT_F32, 1.f, ids, weights, plan, stream);
 }
 
 template <typename TA, typename TW, typename TC>

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const TX* __rest
 
 // out[t, g*n + i] = gate_after * w[g*n+i] * v / sqrt(mean_i(v^2) + eps), v = x[t, g*n + i] * gate_before, per group g of n
 // columns.  gate kinds: 0 none, 1 SiLU(gate) multiplied in before the statistics, 2 sigmoid(gate) multiplied in after the
-// weight.  groups == 0: no normalisation (gate only).  x and gate are column slices (leading dimensions given) of fp32 buffers.
+// weight, 3 SiLU(gate) multiplied in after the weight.  groups == 0: no normalisation (gate only).  x and gate are column slices (leading dimensions given) of fp32 buffers.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kRowThreads) group_rmsnorm_gate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ gate,
                                                                          int64_t ldg, int gate_kind, const TP* __restrict__ w, int groups, int n,
@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(kRowThreads) group_rmsnorm_gate_kernel(const f
     v *= rstd;
     if (w) v *= ldf(w + c);
     if (gate_kind == 2) v *= sigmoid_f(gate[t * ldg + c]);
+    else if (gate_kind == 3) v *= silu_f(gate[t * ldg + c]);
     stf(out + t * ldo + c, v);
   }
 }
@@ -165,6 +166,52 @@ __global__ void __launch_bounds__(kRowThreads) rms_add_kernel(const float* __res
   }
   const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
   for (int i = threadIdx.x; i < W; i += kRowThreads) resid[t * W + i] += y[t * W + i] * rstd * ldf(w + i);
+}
+
+// resid[t] += v / sqrt(mean(v^2) + eps) * w with v = y[t] * sigmoid(gate[t]) (gate NULL: v = y[t]): a sublayer's result, gated per
+// channel, normalised and added to the fp32 stream.  `typed`, when given, also receives the updated row in the projections' type.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) gated_rms_add_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+                                                                    const T* __restrict__ w, float* __restrict__ resid, T* __restrict__ typed, int W,
+                                                                    float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    float v = y[t * W + i];
+    if (gate) v *= sigmoid_f(gate[t * W + i]);
+    row[i] = v;
+    q += v * v;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float r = resid[t * W + i] + row[i] * rstd * ldf(w + i);
+    resid[t * W + i] = r;
+    if (typed) stf(typed + t * W + i, r);
+  }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) stf(out + i, x[i]);
+}
+
+// out = act(g) * u over rows [g | u]; act 0: SiLU, 1: GELU (tanh form)
+template <typename T, int ACT>
+__global__ void ff_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * F;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / F, c = i % F;
+    const float g = ldf(gu + r * 2 * F + c), u = ldf(gu + r * 2 * F + F + c);
+    stf(out + i, (ACT == 1 ? gelu_tanh_f(g) : silu_f(g)) * u);
+  }
 }
 
 }  // namespace seq
@@ -267,6 +314,49 @@ extern "C" int b200_seq_rms_add(const float* y, const void* w, int dt, float* re
   if (T == 0) return B200_OK;
   B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((rms_add_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, y, (const E*)w, resid,
                                        (int)W, eps));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_gated_rms_add(const float* y, const float* gate, const void* w, int dt, float* resid, void* typed, int64_t T, int64_t W,
+                                      float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  if (W * 4 > 160 * 1024) { b200_set_last_error("seq_gated_rms_add: row too wide"); return B200_ERR_ARG; }
+#define GRA(E)                                                                                                                          \
+  do {                                                                                                                                  \
+    static bool cfg = false;                                                                                                            \
+    if (!cfg) { cudaFuncSetAttribute(gated_rms_add_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }   \
+    B200_LAUNCH((gated_rms_add_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), (size_t)W * 4, (cudaStream_t)stream, y, gate, (const E*)w, \
+                resid, (E*)typed, (int)W, eps);                                                                                         \
+  } while (0)
+  if (dt == B200_DT_F32) GRA(float);
+  else if (dt == B200_DT_BF16) GRA(__nv_bfloat16);
+  else { b200_set_last_error("unknown element type"); return B200_ERR_ARG; }
+#undef GRA
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_cast_rows(const float* x, void* out, int dt, int64_t n, void* stream) {
+  if (n == 0) return B200_OK;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((cast_rows_kernel<E>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, (E*)out, n));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// act 0: SiLU(g) * u, 1: GELU_tanh(g) * u
+extern "C" int b200_seq_ff_gate(const void* gu, void* out, int dt, int64_t rows, int64_t F, int act, void* stream) {
+  if (rows == 0 || F == 0) return B200_OK;
+  int64_t blocks = (rows * F + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act == 1)
+    B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((ff_gate_kernel<E, 1>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const E*)gu, (E*)out,
+                                         rows, (int)F));
+  else
+    B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((ff_gate_kernel<E, 0>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const E*)gu, (E*)out,
+                                         rows, (int)F));
   b200_count_launches(1);
   return B200_OK;
 }

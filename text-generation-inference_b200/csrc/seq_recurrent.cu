@@ -5,6 +5,9 @@
 //   mlstm_scan_kernel (matrix memory with exponential gating)  m_t = max(f_t + m_(t-1), i_t),
 //                     S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T, n_t likewise with k_t alone,
 //                     y_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6); i_t = cap tanh(raw/cap), f_t = logsigmoid(cap tanh(raw/cap)).
+//   delta_scan_kernel (gated delta rule)  S <- g_t S, u_t = beta_t (v_t - S^T k_t), S <- S + k_t u_t^T, y_t = S^T q_t (the read-out sees the
+//                     token's own write); q_t, k_t unit vectors (x / sqrt(sum x^2 + 1e-6)), q_t times q_scale; beta_t = sigmoid(raw),
+//                     g_t = exp(-exp(A_log) softplus(raw + dt_bias)); q / k shared by the heads of a group.
 //   causal_conv_silu_kernel / conv_state_update_kernel: short depth-wise causal convolution whose last taps-1 inputs are state.
 //
 // One block owns (sequence, head, 32 value columns) and walks the sequence's tokens of this step in order, whether they are a
@@ -220,6 +223,120 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
   if (blockIdx.z == 0 && threadIdx.x == 0) m_state[slot * H + h] = m;
 }
 
+// Gated delta rule.  c: the convolved, activated [q | k | v] rows; raw: the rows holding the write-strength and decay projections.
+template <typename TP, int KMAX>
+__global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(
+    const float* __restrict__ c, int64_t ldc, int col_q, int col_k, int col_v, const float* __restrict__ raw, int64_t ldr, int col_b, int col_a,
+    const TP* __restrict__ A_log, const TP* __restrict__ dt_bias, float q_scale, float* __restrict__ S_state, const int32_t* __restrict__ state_slots,
+    const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ y, int64_t ld_y, int H, int dk, int dv,
+    int heads_per_group) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* qs = sm;                       // [kChunk][dk]
+  float* kk = qs + kChunk * dk;         // [kChunk][dk]
+  float* vs = kk + kChunk * dk;         // [kChunk][kCols]
+  float* ys = vs + kChunk * kCols;      // [kChunk][kCols]
+  float* bt = ys + kChunk * kCols;      // [kChunk] write strength
+  float* dc = bt + kChunk;              // [kChunk] decay
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
+  const int g = h / heads_per_group;
+  const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (t_begin >= t_end) return;
+  const bool fresh = position_ids[t_begin] == 0;
+  float* Sp = S_state + ((int64_t)state_slots[b] * H + h) * dk * dv;
+  float S[KMAX];
+  float* stage = dc + kChunk;  // [dk][kCols + 1]
+  if (!fresh) {
+    for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+      const int n = idx / kCols, cc = idx % kCols;
+      stage[n * (kCols + 1) + cc] = (v0 + cc < dv) ? Sp[(int64_t)n * dv + v0 + cc] : 0.f;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    S[i] = (!fresh && n < dk) ? stage[n * (kCols + 1) + col] : 0.f;
+  }
+  const float A = expf(ldf(A_log + h)), bias = ldf(dt_bias + h);
+  for (int t0 = t_begin; t0 < t_end; t0 += kChunk) {
+    const int nt = min(kChunk, t_end - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * dk; idx += kScanThreads) {
+      const int tt = idx / dk, n = idx % dk;
+      const float* row = c + (int64_t)(t0 + tt) * ldc;
+      qs[idx] = row[col_q + g * dk + n];
+      kk[idx] = row[col_k + g * dk + n];
+    }
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, cc = idx % kCols;
+      vs[idx] = (v0 + cc < dv) ? c[(int64_t)(t0 + tt) * ldc + col_v + h * dv + v0 + cc] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const float* row = raw + (int64_t)(t0 + threadIdx.x) * ldr;
+      bt[threadIdx.x] = sigmoid_f(row[col_b + h]);
+      dc[threadIdx.x] = expf(-A * softplus_f(row[col_a + h] + bias));
+    }
+    __syncthreads();
+    for (int tt = warp_id(); tt < nt; tt += kScanThreads / 32) {  // unit length, one warp per token
+      float sq = 0.f, sk = 0.f;
+      for (int n = lane_id(); n < dk; n += 32) {
+        sq = fmaf(qs[tt * dk + n], qs[tt * dk + n], sq);
+        sk = fmaf(kk[tt * dk + n], kk[tt * dk + n], sk);
+      }
+      const float rq = q_scale / sqrtf(warp_sum(sq) + 1e-6f), rk = 1.f / sqrtf(warp_sum(sk) + 1e-6f);
+      for (int n = lane_id(); n < dk; n += 32) {
+        qs[tt * dk + n] *= rq;
+        kk[tt * dk + n] *= rk;
+      }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float a = dc[tt];
+      float pred = 0.f;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) {
+          S[i] *= a;
+          pred = fmaf(S[i], kk[tt * dk + n], pred);
+        }
+      }
+      pred = group8_sum(pred);
+      const float u = bt[tt] * (vs[tt * kCols + col] - pred);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) {
+          S[i] = fmaf(kk[tt * dk + n], u, S[i]);
+          o = fmaf(S[i], qs[tt * dk + n], o);
+        }
+      }
+      o = group8_sum(o);
+      if (ks == 0) ys[tt * kCols + col] = o;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, cc = idx % kCols;
+      if (v0 + cc < dv) y[(int64_t)(t0 + tt) * ld_y + h * dv + v0 + cc] = ys[idx];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    if (n < dk) stage[n * (kCols + 1) + col] = S[i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+    const int n = idx / kCols, cc = idx % kCols;
+    if (v0 + cc < dv) Sp[(int64_t)n * dv + v0 + cc] = stage[n * (kCols + 1) + cc];
+  }
+}
+
 constexpr int kMaxTaps = 8;
 
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in(p - (taps-1) + j)), p the token's position; inputs before this step's first token
@@ -372,4 +489,37 @@ extern "C" int b200_seq_mlstm_scan(const float* proj, int64_t ld, int col_q, int
   else if (dk <= 128) ML(16);
   else ML(32);
 #undef ML
+}
+
+template <typename TP, int KMAX>
+static int launch_delta(const float* c, int64_t ldc, int col_q, int col_k, int col_v, const float* raw, int64_t ldr, int col_b, int col_a,
+                        const void* A_log, const void* dt_bias, float q_scale, float* S_state, const int32_t* state_slots, const int32_t* cu_q,
+                        const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, int hpg, cudaStream_t st) {
+  const size_t smem = ((size_t)2 * kChunk * dk + 2 * kChunk * kCols + 2 * kChunk + (size_t)dk * (kCols + 1)) * 4;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(delta_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); cfg = true; }
+  dim3 grid((unsigned)B, (unsigned)H, (unsigned)((dv + kCols - 1) / kCols));
+  B200_LAUNCH((delta_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, c, ldc, col_q, col_k, col_v, raw, ldr, col_b, col_a,
+              (const TP*)A_log, (const TP*)dt_bias, q_scale, S_state, state_slots, cu_q, position_ids, y, ld_y, H, dk, dv, hpg);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// c fp32 [T, ldc]: activated q / k (kv_heads x dk each) and v (H x dv) columns; raw fp32 [T, ldr]: write-strength and decay logits, one per
+// head; A_log, dt_bias [H] of element type dt; S_state fp32 [slots, H, dk, dv] advanced in place -> y fp32 [T, H * dv]
+extern "C" int b200_seq_delta_scan(const float* c, int64_t ldc, int col_q, int col_k, int col_v, const float* raw, int64_t ldr, int col_b, int col_a,
+                                   const void* A_log, const void* dt_bias, int dt, float q_scale, float* S_state, const int32_t* state_slots,
+                                   const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int kv_heads, int dk,
+                                   int dv, void* stream) {
+  if (B == 0) return B200_OK;
+  if (kv_heads <= 0 || H % kv_heads != 0 || dk > 256) { b200_set_last_error("seq_delta_scan: need heads % kv_heads == 0 and key size <= 256"); return B200_ERR_ARG; }
+  const int hpg = H / kv_heads;
+  cudaStream_t st = (cudaStream_t)stream;
+#define DL(K)                                                                                                                                  \
+  B200_SEQ_DISPATCH(dt, E, return (launch_delta<E, K>(c, ldc, col_q, col_k, col_v, raw, ldr, col_b, col_a, A_log, dt_bias, q_scale, S_state,    \
+                                                     state_slots, cu_q, position_ids, y, ld_y, B, H, dk, dv, hpg, st)))
+  if (dk <= 64) DL(8);
+  else if (dk <= 128) DL(16);
+  else DL(32);
+#undef DL
 }

@@ -30,6 +30,7 @@ class RaggedDecoderForCausalLM(nn.Module):
     ragged_steps = True           # FlashCausalLM.step_ragged: any mix of prompts, portions and decoded tokens in one batch
     logits_dtype = torch.float32
     scratch = _NoScratch()        # nothing of the fused step is ever re-allocated
+    logit_scale = 1.0             # logits = head(final_norm(x)) * logit_scale
 
     @property
     def fused_greedy_enabled(self) -> bool:
@@ -61,7 +62,7 @@ class RaggedDecoderForCausalLM(nn.Module):
     def prepare_positions(self, max_s: int) -> None:
         """grows whatever per-position tables the layers keep, so that nothing is allocated inside a captured graph"""
         for layer in self.model.layers:
-            if hasattr(layer.mixer, "rotary"):
+            if getattr(layer.mixer, "rotary", None) is not None:
                 layer.mixer.rotary.tables(int(max_s) + 1, self.device)
 
     def make_cache_manager(self, dtype, device, num_blocks: Optional[int], num_state_slots: Optional[int]) -> HybridCacheManager:
@@ -119,4 +120,6 @@ class RaggedDecoderForCausalLM(nn.Module):
         if lm_head_indices is not None:
             x = x[lm_head_indices].contiguous()
         logits = ops.linear(self.model.final_norm(x), self.head, out_dtype=torch.float32)
+        if self.logit_scale != 1.0:
+            logits.mul_(self.logit_scale)
         return logits, kv

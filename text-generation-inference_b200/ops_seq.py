@@ -136,13 +136,14 @@ def layernorm_into_residual(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, e
     return (copy if copy is not None else residual) if typed_copy else None
 
 
-GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER = 0, 1, 2
+GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER, GATE_SILU_AFTER = 0, 1, 2, 3
 
 
 def group_rmsnorm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], groups: int, eps: float, out_dtype: torch.dtype,
                        gate: Optional[torch.Tensor] = None, gate_kind: int = GATE_NONE) -> torch.Tensor:
     """x, gate: fp32 [T, C] column slices.  Per group of C / groups columns: v / sqrt(mean(v^2) + eps) * weight, with the gate
-    multiplied in before the statistics (SiLU) or after the weight (sigmoid).  groups == 0: no normalisation."""
+    multiplied in before the statistics (SiLU) or after the weight (sigmoid, or SiLU with GATE_SILU_AFTER).  groups == 0: no
+    normalisation.  `weight` has one entry per column."""
     _cuda(x, weight, gate)
     assert x.dtype == torch.float32 and x.stride(1) == 1 and (gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1))
     T, C = x.shape
@@ -355,16 +356,24 @@ class MoeRouting:
     plan: torch.Tensor      # int32 workspace (b200_seq_moe_plan_ints)
 
 
-def moe_route(logits: torch.Tensor, top: int) -> MoeRouting:
-    """logits fp32 [T, E] -> the `top` largest per token (ties: the lower expert), weights = soft-max over the picked logits."""
-    _cuda(logits)
+def moe_route(logits: torch.Tensor, top: int, *, sigmoid_scores: bool = False, correction: Optional[torch.Tensor] = None,
+              weight_scale: float = 1.0) -> MoeRouting:
+    """logits fp32 [T, E] -> the `top` largest per token (ties: the lower expert), weights = soft-max over the picked logits.
+    sigmoid_scores: the picks are the largest sigmoid(logit) + correction[expert]; the weights are the picked sigmoid(logit)
+    divided by their sum and multiplied by weight_scale."""
+    _cuda(logits, correction)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     T, E = logits.shape
     lib = _lib.load_seq()
     ids = torch.empty(T, top, dtype=torch.int32, device=logits.device)
     weights = torch.empty(T, top, dtype=torch.float32, device=logits.device)
     plan = torch.empty(int(lib.b200_seq_moe_plan_ints(T, E, top)), dtype=torch.int32, device=logits.device)
-    _lib.check_seq(lib.b200_seq_moe_route(_ptr(logits), T, E, top, _ptr(ids), _ptr(weights), _ptr(plan), _stream()), "seq_moe_route")
+    if sigmoid_scores:
+        assert correction is None or (correction.is_contiguous() and correction.shape == (E,))
+        _lib.check_seq(lib.b200_seq_moe_route_scored(_ptr(logits), T, E, top, 1, _ptr(correction), 1 if correction is None else _dt(correction),
+                                                     float(weight_scale), _ptr(ids), _ptr(weights), _ptr(plan), _stream()), "seq_moe_route")
+    else:
+        _lib.check_seq(lib.b200_seq_moe_route(_ptr(logits), T, E, top, _ptr(ids), _ptr(weights), _ptr(plan), _stream()), "seq_moe_route")
     return MoeRouting(T, E, top, ids, weights, plan)
 
 
@@ -403,3 +412,91 @@ def moe_combine_add(resid: torch.Tensor, mix: Optional[torch.Tensor], y: Optiona
     _lib.check_seq(_lib.load_seq().b200_seq_moe_combine_add(
         _ptr(resid), _ptr(mix), _ptr(y), 0 if y is None else y.stride(0), None if y is None else _ptr(r.weights), None if y is None else _ptr(r.plan),
         T, 0 if y is None else r.experts, 0 if y is None else r.top, W, _stream()), "seq_moe_combine_add")
+
+
+def gated_rms_add(resid: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], w: torch.Tensor, eps: float,
+                  typed_copy: bool = False) -> Optional[torch.Tensor]:
+    """resid (fp32, in place) += v / sqrt(mean(v^2) + eps) * w with v = y * sigmoid(gate) (gate None: v = y); y and gate fp32 [T, W].
+    typed_copy: also returns the updated stream in w's element type (the input of the next projection); for float32 that is the
+    stream itself."""
+    _cuda(resid, y, gate, w)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous() and y.shape == resid.shape
+    assert gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and gate.shape == resid.shape)
+    copy = torch.empty(resid.shape, dtype=w.dtype, device=resid.device) if typed_copy and w.dtype != torch.float32 else None
+    _lib.check_seq(_lib.load_seq().b200_seq_gated_rms_add(_ptr(y), _ptr(gate), _ptr(w), _dt(w), _ptr(resid), _ptr(copy), resid.shape[0],
+                                                          resid.shape[1], float(eps), _stream()), "seq_gated_rms_add")
+    return (copy if copy is not None else resid) if typed_copy else None
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """the fp32 stream in the projections' element type (float32: the stream itself)"""
+    _cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_cast_rows(_ptr(x), _ptr(out), _dt(dtype), x.numel(), _stream()), "seq_cast_rows")
+    return out
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def ff_gate(gate_up: torch.Tensor, act: int) -> torch.Tensor:
+    """[T, 2F] = [g | u] -> [T, F]: act(g) * u with act SiLU or the tanh form of GELU, evaluated in fp32."""
+    _cuda(gate_up)
+    assert gate_up.is_contiguous()
+    T, F2 = gate_up.shape
+    out = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_ff_gate(_ptr(gate_up), _ptr(out), _dt(gate_up), T, F2 // 2, int(act), _stream()), "seq_ff_gate")
+    return out
+
+
+def delta_scan(c: torch.Tensor, col_q: int, col_k: int, col_v: int, raw: torch.Tensor, col_b: int, col_a: int, A_log: torch.Tensor,
+               dt_bias: torch.Tensor, q_scale: float, S: torch.Tensor, step: RaggedStep, H: int, kv_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """Gated delta rule -> y fp32 [T, H * dv]; S fp32 [slots, H, dk, dv] advanced in place.  c fp32: activated q / k (kv_heads x dk
+    each) and v (H x dv) columns; raw fp32: write-strength logits at col_b and decay logits at col_a, one per head."""
+    _cuda(c, raw, S, A_log, dt_bias)
+    assert c.dtype == torch.float32 and raw.dtype == torch.float32 and S.dtype == torch.float32 and S.is_contiguous()
+    assert c.stride(1) == 1 and raw.stride(1) == 1 and A_log.dtype == dt_bias.dtype
+    y = torch.empty(step.T, H * dv, dtype=torch.float32, device=c.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_delta_scan(
+        _ptr(c), c.stride(0), col_q, col_k, col_v, _ptr(raw), raw.stride(0), col_b, col_a, _ptr(A_log), _ptr(dt_bias), _dt(A_log), float(q_scale),
+        _ptr(S), _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(y), y.stride(0), step.B, H, kv_heads, dk, dv, _stream()),
+        "seq_delta_scan")
+    return y
+
+
+def qk_rot_prepare(src: torch.Tensor, *, col_q: int, col_k: int, col_v: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                   q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], whole_norm: bool, eps: float, cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], rot: int, step: RaggedStep, cache: torch.Tensor, k_off: int, v_off: int) -> torch.Tensor:
+    """src fp32 [T, C] = [q | k | v] projections: RMS norm over the whole q and the whole k projection (whole_norm), rotation of the
+    first `rot` columns of every head in the rotate-half layout with the cos / sin tables, keys and values into the token's row of
+    `cache` [blocks, page, row] (token-major: keys of all key heads from k_off, values from v_off) -> queries fp32 [T, heads, dim]."""
+    _cuda(src, cache, q_norm_w, k_norm_w, cos, sin)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and cache.is_contiguous()
+    assert rot == 0 or (cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == rot // 2)
+    q = torch.empty(step.T, heads, dim, dtype=torch.float32, device=src.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_qk_rot_prepare(
+        _ptr(src), src.stride(0), col_q, col_k, col_v, heads, kv_heads, dim, vdim, _ptr(q_norm_w), _ptr(k_norm_w), int(whole_norm), float(eps),
+        _ptr(cos), _ptr(sin), int(rot), _ptr(step.position_ids), _ptr(step.slot_mapping), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off,
+        _ptr(q), step.T, _stream()), "seq_qk_rot_prepare")
+    return q
+
+
+def talk_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, kv_heads: int, vdim: int, k_off: int, v_off: int, scale: float,
+              talk: Optional[torch.Tensor] = None, chunk: int = 0, window: int = 0) -> torch.Tensor:
+    """q fp32 [T, heads, dim]; cache [blocks, page, row] token-major as `qk_rot_prepare` writes it -> fp32 [T, heads, vdim]: attention
+    of every token over its own sequence's cache rows; the scaled scores of all heads are mixed by talk fp32 [heads, heads]
+    (s'_h = sum_g talk[h, g] s_g) before the soft-max.  chunk > 0: a query sees only keys of its own chunk of `chunk` positions
+    (counted from position 0); window > 0: only the last `window` keys."""
+    _cuda(q, cache, talk)
+    T, H, d = q.shape
+    assert q.is_contiguous() and cache.is_contiguous() and q.dtype == torch.float32
+    assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (H, H))
+    out = torch.empty(T, H, vdim, dtype=torch.float32, device=q.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_talk_attn(
+        _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
+        _ptr(step.seq_of_token), _ptr(step.cu_q), step.B, _ptr(step.position_ids), _ptr(talk), _ptr(out), T, H, kv_heads, d, vdim, int(chunk),
+        int(window), float(scale), cache.shape[1], _stream()), "seq_talk_attn")
+    return out

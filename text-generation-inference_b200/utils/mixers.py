@@ -2,7 +2,8 @@
 family can compose them: latent attention over a paged latent cache (sliding window, rotary part with optional YaRN frequency
 scaling), the selective state-space mixer (Mamba-2 form), the matrix-memory mixer (mLSTM), differential attention (two soft-max
 maps per head, short convolutions after the projections, optionally over another layer's keys and values), attention with a
-learned bias per log-spaced distance bucket, and the feed-forward layers (clamped gated MLP, routed experts).
+learned bias per log-spaced distance bucket, the gated delta rule, attention with head-mixed scores under a chunked mask, and
+the feed-forward layers (clamped gated MLP, gated MLP with biases, routed experts with an optional shared expert).
 
 A mixer declares what it keeps per sequence (`cache_spec`): a row of the paged cache per token, or fp32 state tensors in a
 state slot.  `forward(h, step, store)` takes the normed hidden states of a ragged step (ops_seq.RaggedStep: any mix of whole
@@ -28,7 +29,8 @@ def _need_single_rank(weights, what: str):
 
 
 class ScaledRotaryTables:
-    """cos / sin of position * frequency for interleaved-pair rotation, fp32 [positions, dims / 2], grown on demand.
+    """cos / sin of position * frequency of every rotated pair, fp32 [positions, dims / 2], grown on demand (which columns form
+    pair i - neighbours or halves - is the kernel's business).
     frequency_i = base^(-2i/dims).  With `scaling` = {factor, original, fast, slow} (YaRN): pairs that turn more than `fast`
     times over `original` positions keep their frequency, pairs that turn fewer than `slow` times are slowed by `factor`, a
     linear ramp over the pair index in between; cos and sin are multiplied by 0.1 ln(factor) + 1."""
@@ -295,26 +297,35 @@ class BucketBiasAttention(nn.Module):
 
 
 class RoutedExperts(nn.Module):
-    """Mixture of clamped gated experts: router logits in fp32, the `top` largest per token, weights = soft-max over the picked
-    logits; each expert is down(g' sigmoid(alpha g') (u' + 1)) as in `ClampedGatedMLP`, without biases.  `forward` returns the
+    """Mixture of gated experts without biases: router logits in fp32, `top` experts per token.  Routing rule: the largest logits
+    with weights = soft-max over the picked logits, or (`sigmoid_scores`) the largest sigmoid(logit) + correction with weights =
+    picked sigmoid(logit) / their sum * `weight_scale`.  Expert: down(act(gate x) . up x), act = the clamped form of
+    `ClampedGatedMLP` (`limit` given: g' sigmoid(alpha g') (u' + 1)) or plain SiLU(g) u (`limit` None).  `forward` returns the
     experts' outputs as compact rows (expert by expert) with the routing; `ops.moe_combine_add` sums them into the stream.
-    Tensors under `prefix`: router, e<j>.gate, e<j>.up, e<j>.down."""
+    Tensors under `prefix`: router, [correction,] e<j>.gate, e<j>.up, e<j>.down."""
 
     dense_rows_per_expert = 64   # average rows per expert from which a step runs one dense product per expert
 
-    def __init__(self, prefix: str, weights, *, experts: int, top: int, limit: float, alpha: float = 1.702):
+    def __init__(self, prefix: str, weights, *, experts: int, top: int, limit: Optional[float], alpha: float = 1.702,
+                 sigmoid_scores: bool = False, correction: bool = False, weight_scale: float = 1.0):
         super().__init__()
         _need_single_rank(weights, "RoutedExperts")
-        self.E, self.top, self.limit, self.alpha = int(experts), int(top), float(limit), float(alpha)
+        self.E, self.top, self.limit, self.alpha = int(experts), int(top), None if limit is None else float(limit), float(alpha)
+        self.sigmoid_scores, self.weight_scale = bool(sigmoid_scores), float(weight_scale)
         get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.correction = get("correction").contiguous() if correction else None
         self.w_router = get("router").contiguous()
         self.w_gate_up = torch.stack([torch.cat([get(f"e{e}.gate"), get(f"e{e}.up")], 0) for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([get(f"e{e}.down") for e in range(self.E)]).contiguous()
         if self.w_router.shape[0] != self.E:
             raise ValueError(f"{prefix}.router: one row per expert expected")
 
+    def _act(self, gu: torch.Tensor) -> torch.Tensor:
+        return ops.ff_gate(gu, ops.ACT_SILU) if self.limit is None else ops.ff_clamped_gate(gu, self.limit, self.alpha)
+
     def forward(self, h: torch.Tensor):
-        routing = ops.moe_route(ops.linear(h, self.w_router, out_dtype=torch.float32), self.top)
+        routing = ops.moe_route(ops.linear(h, self.w_router, out_dtype=torch.float32), self.top, sigmoid_scores=self.sigmoid_scores,
+                                correction=self.correction, weight_scale=self.weight_scale)
         rows = h.shape[0] * self.top
         if h.dtype == torch.bfloat16 and rows >= self.dense_rows_per_expert * self.E and not torch.cuda.is_current_stream_capturing():
             # prompts: enough rows per expert for the tcgen05 product (ops.linear) to pay - one product per expert over its run of
@@ -325,12 +336,116 @@ class RoutedExperts(nn.Module):
             for e in range(self.E):
                 if offs[e + 1] > offs[e]:
                     ops.linear(a[offs[e]:offs[e + 1]], self.w_gate_up[e], out=gu[offs[e]:offs[e + 1]])
-            act = ops.ff_clamped_gate(gu, self.limit, self.alpha)
+            act = self._act(gu)
             y = torch.empty(rows, self.w_down.shape[1], dtype=torch.float32, device=h.device)
             for e in range(self.E):
                 if offs[e + 1] > offs[e]:
                     ops.linear(act[offs[e]:offs[e + 1]], self.w_down[e], out=y[offs[e]:offs[e + 1]])
             return y, routing
         gu = ops.moe_linear(h, self.w_gate_up, routing, gather=True, out_dtype=h.dtype)
-        act = ops.ff_clamped_gate(gu, self.limit, self.alpha)
-        return ops.moe_linear(act, self.w_down, routing, gather=False, out_dtype=torch.float32), routing
+        return ops.moe_linear(self._act(gu), self.w_down, routing, gather=False, out_dtype=torch.float32), routing
+
+
+class GatedMLP(nn.Module):
+    """down(act(gate x + b_g) * (up x + b_u)) + b_d with act SiLU or the tanh form of GELU; biases optional.  The result is fp32.
+    Tensors under `prefix`: gate, up, down [, gate.b, up.b, down.b]."""
+
+    def __init__(self, prefix: str, weights, *, activation: str, bias: bool):
+        super().__init__()
+        _need_single_rank(weights, "GatedMLP")
+        if activation not in ("silu", "gelu_tanh"):
+            raise NotImplementedError(f"activation {activation!r}")
+        self.act = ops.ACT_SILU if activation == "silu" else ops.ACT_GELU_TANH
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_gate_up = torch.cat([get("gate"), get("up")], 0).contiguous()
+        self.w_down = get("down").contiguous()
+        self.b_gate_up = torch.cat([get("gate.b"), get("up.b")], 0).contiguous() if bias else None
+        self.b_down = get("down.b").contiguous() if bias else None
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.linear(ops.ff_gate(ops.linear(h, self.w_gate_up, self.b_gate_up), self.act), self.w_down, self.b_down, out_dtype=torch.float32)
+
+
+class GatedDeltaMixer(nn.Module):
+    """Gated delta rule: per head a [dim, vdim] memory S in fp32; every token S <- g S, u = beta (v - S^T k), S <- S + k u^T,
+    o = S^T q (the read-out sees the token's own write).  q / k (kv_heads x dim, shared by heads / kv_heads heads) and v
+    (heads x vdim) pass a depth-wise causal convolution (`conv` taps, no bias) and SiLU; q and k become unit vectors
+    (x / sqrt(sum x^2 + 1e-6)), q times dim^-1/2; beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)).  Each
+    head's o is divided by its RMS, times a weight shared by the heads, times SiLU(W_g h); then the output projection.
+    State per sequence: S and the last conv - 1 convolution inputs, both fp32.
+    Tensors under `prefix`: q, q.conv, k, k.conv, v, v.conv, b, a, A_log, dt_bias, g, norm, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, eps: float):
+        super().__init__()
+        _need_single_rank(weights, "GatedDeltaMixer")
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.d, self.dv, self.taps, self.eps = int(heads), int(kv_heads), int(dim), int(vdim), int(conv), float(eps)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.cqk, self.cv = self.G * self.d, self.H * self.dv
+        self.channels = 2 * self.cqk + self.cv                                            # convolved columns [q | k | v]
+        self.w_in = torch.cat([get(n) for n in ("q", "k", "v", "g", "b", "a")], 0).contiguous()   # -> [q | k | v | gate | beta | decay]
+        self.conv_w = torch.cat([get(f"{n}.conv") for n in ("q", "k", "v")], 0).contiguous()
+        self.A_log, self.dt_bias = get("A_log").contiguous(), get("dt_bias").contiguous()
+        self.norm_w = get("norm").repeat(self.H).contiguous()                            # one entry per column of the heads
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        if self.w_in.shape[0] != self.channels + self.cv + 2 * self.H or self.conv_w.shape != (self.channels, self.taps):
+            raise ValueError(f"{prefix}: projection / convolution shapes do not match the head sizes")
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state={"S": (self.H, self.d, self.dv), "conv": (max(self.taps - 1, 1), self.channels)})
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages, state: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        C, cv, H = self.channels, self.cv, self.H
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        c = ops.causal_conv(u, 0, C, self.conv_w, None, state["conv"], step, act_silu=True)
+        y = ops.delta_scan(c, 0, self.cqk, 2 * self.cqk, u, C + cv, C + cv + H, self.A_log, self.dt_bias, self.d ** -0.5, state["S"], step,
+                           H, self.G, self.d, self.dv)
+        gated = ops.group_rmsnorm_gate(y, self.norm_w, H, self.eps, self.dtype, gate=u[:, C:C + cv], gate_kind=ops.GATE_SILU_AFTER)
+        return ops.linear(gated, self.w_o, out_dtype=torch.float32)
+
+
+class TalkingHeadsAttention(nn.Module):
+    """Grouped-query attention whose scaled scores are mixed over the query heads before the soft-max, s'_h = sum_g talk[h, g] s_g.
+    Queries and keys are RMS-normed over their whole projection (all heads at once, a weight per column) and then rotated on the
+    first `rotary.dims` columns of every head in the rotate-half layout (column i with column i + dims / 2; `rotary` None: no
+    rotation).  Mask: causal, within chunks of `chunk` positions counted from the start of the sequence (None: plain causal),
+    optionally a sliding window.  Cached per token: the rotated keys and the values of all key heads (token-major row).
+    Tensors under `prefix`: q, k, v, q.norm, k.norm, talk, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, rotary: Optional[ScaledRotaryTables],
+                 chunk: Optional[int], eps: float, window: Optional[int] = None, talk: bool = True):
+        super().__init__()
+        _need_single_rank(weights, "TalkingHeadsAttention")
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.d, self.dv = int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.rotary, self.chunk, self.window, self.eps = float(scale), rotary, int(chunk or 0), int(window or 0), float(eps)
+        if rotary is not None and rotary.dims > dim:
+            raise ValueError("rotary dims exceed the head size")
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_in = torch.cat([get("q"), get("k"), get("v")], 0).contiguous()
+        self.q_norm, self.k_norm = get("q.norm").contiguous(), get("k.norm").contiguous()
+        self.talk = get("talk").float().contiguous() if talk else None
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        self.cq, self.ck, self.cv = self.H * self.d, self.G * self.d, self.G * self.dv
+        if self.w_in.shape[0] != self.cq + self.ck + self.cv or (self.talk is not None and self.talk.shape != (self.H, self.H)):
+            raise ValueError(f"{prefix}: projection shapes do not match the head sizes")
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="paged", row_width=self.ck + self.cv)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages: torch.Tensor, state, max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        cos, sin = self.rotary.tables(max_s, h.device) if self.rotary is not None else (None, None)
+        q = ops.qk_rot_prepare(u, col_q=0, col_k=self.cq, col_v=self.cq + self.ck, heads=self.H, kv_heads=self.G, dim=self.d, vdim=self.dv,
+                               q_norm_w=self.q_norm, k_norm_w=self.k_norm, whole_norm=True, eps=self.eps, cos=cos, sin=sin,
+                               rot=self.rotary.dims if self.rotary is not None else 0, step=step, cache=pages, k_off=0, v_off=self.ck)
+        a = ops.talk_attn(q, pages, step, kv_heads=self.G, vdim=self.dv, k_off=0, v_off=self.ck, scale=self.scale, talk=self.talk,
+                          chunk=self.chunk, window=self.window)
+        o = ops.cast_rows(a.view(step.T, self.H * self.dv), self.dtype)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
