@@ -196,3 +196,95 @@ def forward(config: dict, sd: Dict[str, torch.Tensor], tokens: List[int], dtype=
         if residuals is not None:
             residuals.append(x.clone())
     return (unit_rms(x, eps) * sd["final.norm"]) @ sd["head"].T * float(config.get("logit_scale", 1.0))
+
+
+# ------------------------------------------------------------------------------------------------ random models
+def random_config(*, width: int = 40, vocab: int = 72, order=("delta", "attention", "delta", "attention"), weights_of=(None, None, 0, None),
+                  heads=(6, 4), kv_heads=(3, 2), dim=(10, 12), vdim=(14, 20), rot_dims: int = 8, base: float = 100.0, scaling="yarn",
+                  chunk: int = 24, conv: int = 3, mlp=("moe", "dense", "moe", None), experts: int = 5, top: int = 2, ff: int = 24, shared_ff=16,
+                  router_scale: float = 1.5, logit_scale: float = 0.5, eps: float = 1e-5) -> dict:
+    """a small configuration; `heads`, `kv_heads`, `dim`, `vdim` are (attention, delta)"""
+    layers = []
+    for i, kind in enumerate(order):
+        if kind == "attention":
+            rot = {"base": base, "dims": rot_dims}
+            if scaling == "yarn":
+                rot["scaling"] = {"factor": 4.0, "fast": 8.0, "original": 32, "slow": 1.0}
+            mixer = {"dim": dim[0], "heads": heads[0], "kv_heads": kv_heads[0], "vdim": vdim[0], "scale": dim[0] ** -0.5 * 1.6, "rot": rot}
+            if chunk:
+                mixer["mask"] = {"size": chunk}
+        else:
+            mixer = {"conv": conv, "dim": dim[1], "heads": heads[1], "kv_heads": kv_heads[1], "vdim": vdim[1]}
+        f = mlp[i]
+        if f == "dense":
+            f = {"kind": "dense", "ff": ff + 4}
+        elif f == "moe":
+            f = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": router_scale},
+                 "shared": {"ff": shared_ff} if shared_ff else None}
+        layer = {"type": kind, "mixer": mixer, "mlp": f}
+        if weights_of[i] is not None:
+            src = layers[int(weights_of[i])]
+            layer = {"type": src["type"], "mixer": src["mixer"], "mlp": src["mlp"], "weights_of": int(weights_of[i])}
+        layers.append(layer)
+    return {"architecture": "Noganex", "layers": layers, "logit_scale": logit_scale, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+def tensor_shapes(config: dict) -> Dict[str, tuple]:
+    W, V = int(config["width"]), int(config["vocab"])
+    out = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, layer in enumerate(config["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        m, pre = layer["mixer"], f"l{i}"
+        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        out.update({f"{pre}.norm1": (W,), f"{pre}.rg1": (W, W), f"{pre}.rg1.b": (W,)})
+        if layer["type"] == "attention":
+            mix = {"q": (H * d, W), "k": (G * d, W), "v": (G * dv, W), "q.norm": (H * d,), "k.norm": (G * d,), "talk": (H, H), "o": (W, H * dv)}
+        else:
+            t = int(m["conv"])
+            mix = {"q": (G * d, W), "q.conv": (G * d, t), "k": (G * d, W), "k.conv": (G * d, t), "v": (H * dv, W), "v.conv": (H * dv, t),
+                   "b": (H, W), "a": (H, W), "A_log": (H,), "dt_bias": (H,), "g": (H * dv, W), "norm": (dv,), "o": (W, H * dv)}
+        out.update({f"{pre}.mix.{k}": v for k, v in mix.items()})
+        f = layer.get("mlp")
+        if not f:
+            continue
+        out.update({f"{pre}.norm2": (W,), f"{pre}.rg2": (W, W), f"{pre}.rg2.b": (W,)})
+        if f["kind"] == "dense":
+            n = int(f["ff"])
+            out.update({f"{pre}.mlp.gate": (n, W), f"{pre}.mlp.gate.b": (n,), f"{pre}.mlp.up": (n, W), f"{pre}.mlp.up.b": (n,),
+                        f"{pre}.mlp.down": (W, n), f"{pre}.mlp.down.b": (W,)})
+        else:
+            E, n = int(f["router"]["experts"]), int(f["expert"]["ff"])
+            out.update({f"{pre}.mlp.router": (E, W), f"{pre}.mlp.correction": (E,)})
+            for e in range(E):
+                out.update({f"{pre}.mlp.e{e}.gate": (n, W), f"{pre}.mlp.e{e}.up": (n, W), f"{pre}.mlp.e{e}.down": (W, n)})
+            if f.get("shared"):
+                n = int(f["shared"]["ff"])
+                out.update({f"{pre}.mlp.shared.gate": (n, W), f"{pre}.mlp.shared.up": (n, W), f"{pre}.mlp.shared.down": (W, n)})
+    return out
+
+
+def random_state_dict(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """weights that are exactly representable in bfloat16, so that every element type starts from the same numbers"""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.split(".")[-1]
+        if name.endswith(".talk"):
+            t = torch.eye(shape[0]) + torch.randn(shape, generator=g) * 0.35
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g) * 0.6
+        elif leaf == "correction":
+            t = torch.randn(shape, generator=g) * 0.3
+        elif leaf == "A_log":
+            t = torch.randn(shape, generator=g) * 0.5 - 1.0
+        elif leaf == "dt_bias":
+            t = torch.randn(shape, generator=g) * 0.5
+        elif leaf == "b" and len(shape) == 1:
+            t = torch.randn(shape, generator=g) * 0.5
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) * ((0.7 if name == "embed" else 1.5 / math.sqrt(shape[1])))
+        else:  # norm weights
+            t = 1.0 + torch.randn(shape, generator=g) * 0.3
+        sd[name] = t.to(torch.bfloat16).to(torch.float32)
+    return sd
