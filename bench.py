@@ -1074,6 +1074,195 @@ def run_dubesun_compare(args):
     return 0
 
 
+def _stream_family_measure(raw, cfg, op_names, PB, PL, DB, DL, K, Wm, timed, lib):
+    """one fp32-stream family through the engine: prefill PB x PL and decode DB sequences at context DL, as --dubesun-compare measures
+    them -> dict of timings (ms per call, per op family, per kernel of the graph-replayed decode step) and the decode step's routings"""
+    import torch
+    from tgis_b200 import ops_seq
+    from tgis_b200.inference_engine import InferenceEngine
+    from tgis_b200.models.flash_causal_lm import FlashCausalLM
+    from tgis_b200.utils.dist import FakeGroup
+    from tgis_b200.utils.synthetic import SyntheticHybridWeights, make_tokenizer
+    dev = torch.device("cuda", 0)
+    weights = SyntheticHybridWeights(raw, dev, torch.bfloat16, FakeGroup(0, 1))
+    engine = InferenceEngine("<synthetic>", None, torch.bfloat16, None, cfg, None, weights=weights, tokenizer=make_tokenizer(cfg.vocab_size))
+    model = FlashCausalLM("<synthetic>", None, "tgis_native", torch.bfloat16, None, cfg, engine=engine,
+                          num_kv_blocks=(DB + PB) * ((DL + 64) // 16 + 2), num_state_slots=DB + PB)
+    g = torch.Generator().manual_seed(0)
+    prompt = lambda n, L: [torch.randint(4, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(n)]  # noqa: E731
+    prompts_p = prompt(PB, PL)
+
+    def prefill_once():
+        sids, _ = model.step_ragged([None] * PB, prompts_p, [PL * (i + 1) - 1 for i in range(PB)])
+        model.kv_cache_manager.free_sequences(sids)
+    for _ in range(Wm):
+        prefill_once()
+    pre_ms = timed(prefill_once, K)
+    log = []
+    saved = _timed_ops(ops_seq, op_names, log)
+    prefill_once()
+    pre_ops = _by_op(log)
+    for n, fn in saved.items():
+        setattr(ops_seq, n, fn)
+    sids, _ = model.step_ragged([None] * DB, prompt(DB, DL), [])
+    nxt = [[t[0]] for t in prompt(DB, 1)]
+
+    def decode_once():
+        model.step_ragged(sids, nxt, None)
+    for _ in range(Wm):
+        decode_once()
+    dec_ms = timed(decode_once, K)
+    log, routes = [], []
+    route = ops_seq.moe_route
+    ops_seq.moe_route = lambda *a, **k: (routes.append(route(*a, **k)), routes[-1])[1]
+    saved = _timed_ops(ops_seq, op_names, log)
+    decode_once()
+    dec_ops = _by_op(log)
+    for n, fn in saved.items():
+        setattr(ops_seq, n, fn)
+    ops_seq.moe_route = route
+    picked = sum(len(set(r.ids.flatten().tolist())) for r in routes)
+    model.kv_cache_manager.free_sequences(sids)
+    with torch.inference_mode():   # the serving path: from_pb -> generate_token, plain greedy, replayed as one CUDA graph
+        gpb = make_batch_pb(DB, DL, Wm + K + 8)
+        for r, toks in zip(gpb.requests, prompt(DB, DL)):
+            r.inputs = " ".join(f"<tok{t}>" for t in toks)
+        gbatch, _ = model.batch_type.from_pb(gpb, model.tokenizer, torch.bfloat16, model.device, None, None, True)
+        model.generate_token(gbatch, first=True)
+        for _ in range(Wm):
+            model.generate_token(gbatch)
+        graph_ms = timed(lambda: model.generate_token(gbatch), K)
+        dec_k, dec_total = _traced_decode_step(model, gbatch, lib)
+        model.kv_cache_manager.free_sequences(gbatch.sequence_ids)
+    del model, engine, weights
+    gc.collect()
+    torch.cuda.empty_cache()
+    return {"pre_ms": pre_ms, "pre_ops": pre_ops, "dec_ms": dec_ms, "dec_ops": dec_ops, "graph_ms": graph_ms, "dec_k": dec_k, "dec_total": dec_total,
+            "picked": picked}
+
+
+def run_noganex_compare(args):
+    """Noganex (bfloat16) beside Dubesun (bfloat16), the closest family of the engine (fp32 stream, attention over a paged cache, short
+    convolutions, routed experts), at equal width and depth on random weights: prefill of 4 x 1024 tokens and decode of 32 sequences at
+    context 1024, measured as --dubesun-compare measures its pair, with the achieved FLOP/s or bytes/s of the kernels that carry a step
+    against the measured peaks."""
+    import torch
+    import tgis_b200  # noqa: F401
+    from tgis_b200 import _lib as _libmod
+    from tgis_b200.models.custom_modeling import dubesun_modeling, noganex_modeling
+    from tgis_b200.utils.synthetic import dubesun_config, noganex_config
+
+    pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        pk = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    PB, PL, DB, DL = 4, 1024, 32, 1024
+    K, Wm = max(args.steps // 4, 4), args.warmup
+    ctx = DL + Wm + K + 2
+    lib = _libmod.load_seq()
+    results = []
+
+    def timed(fn, n):
+        total = 0.0
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / n
+
+    def common(name, raw, r, kernels, extra):
+        out = {"model": name, "dtype": "bf16", "layers": len(raw["layers"]), "prefill_tokens_per_s": PB * PL / (r["pre_ms"] * 1e-3),
+               "decode_tokens_per_s": DB / (r["dec_ms"] * 1e-3), "prefill_ms": r["pre_ms"], "decode_ms_per_step": r["dec_ms"],
+               "decode_graph_tokens_per_s": DB / (r["graph_ms"] * 1e-3), "decode_graph_ms_per_step": r["graph_ms"],
+               "prefill_ms_by_op": {k: round(v, 4) for k, v in r["pre_ops"].items()},
+               "decode_ms_by_op": {k: round(v, 4) for k, v in r["dec_ops"].items()},
+               "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(r["dec_k"].items(), key=lambda kv: -kv[1])},
+               "decode_graph_traced_us": r["dec_total"], "kernels": kernels}
+        out.update(extra)
+        return out
+
+    def us(dec_k, *prefixes):
+        return sum(v for k, v in dec_k.items() if k.startswith(prefixes))
+
+    widths = (2048, 4096) if not args.layers else (2048,)
+    for width in widths:
+        # ---------------------------------------------------------------- Noganex
+        raw = noganex_config(f"noganex-w{width}")
+        names = ["linear", "embed_scale", "cast_rows", "rmsnorm_rows", "gated_rms_add", "causal_conv", "delta_scan", "qk_rot_prepare", "talk_attn",
+                 "group_rmsnorm_gate", "moe_route", "moe_gather_rows", "moe_linear", "ff_gate", "moe_combine_add"]
+        r = _stream_family_measure(raw, noganex_modeling.NoganexConfig(raw), names, PB, PL, DB, DL, K, Wm, timed, lib)
+        shapes = noganex_modeling.tensor_shapes(raw)
+        attn = [l["mixer"] for l in raw["layers"] if l["type"] == "attention"]
+        delta = [l["mixer"] for l in raw["layers"] if l["type"] == "delta"]
+        attn_flops = sum(PB * (PL * (PL + 1) // 2) * m["heads"] * (m["dim"] + m["vdim"] + m["heads"]) * 2 for m in attn)
+        attn_row = sum(m["kv_heads"] * (m["dim"] + m["vdim"]) for m in attn)       # elements a decoding token reads per cached token
+        state_b = sum(m["heads"] * m["dim"] * m["vdim"] * 4 * 2 for m in delta)    # state read + written per sequence and step
+        moes = [l["mlp"] for l in raw["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe"]
+        expert_w = 3 * width * moes[0]["expert"]["ff"]
+        top = moes[0]["router"]["top"]
+        dense_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1] if ".mlp.e" not in n and n not in ("embed", "head"))
+        head_w = shapes["head"][0] * shapes["head"][1]
+        lin_flops = 2 * PB * PL * (dense_w + len(moes) * top * expert_w) + 2 * PB * head_w
+        a_us, s_us, m_us = us(r["dec_k"], "talk_attn"), us(r["dec_k"], "delta_scan"), r["dec_k"].get("moe_linear_mma_kernel", 0.0)
+        g_us = r["dec_k"].get("gemm_f16_kernel", 0.0)
+        kernels = {
+            "talk_attn prefill": {"ms": r["pre_ops"]["talk_attn"], "tflops": attn_flops / r["pre_ops"]["talk_attn"] / 1e9,
+                                  "of_measured_tensor": attn_flops / (r["pre_ops"]["talk_attn"] * 1e-3) / tens},
+            "talk_attn decode": {"us": a_us, "of_measured_hbm": DB * ctx * attn_row * 2 / (max(a_us, 1e-9) * 1e-6) / hbm},
+            "delta_scan prefill": {"ms": r["pre_ops"]["delta_scan"], "tokens_per_s_per_layer": PB * PL * len(delta) / (r["pre_ops"]["delta_scan"] * 1e-3)},
+            "delta_scan decode": {"us": s_us, "of_measured_hbm": DB * state_b / (max(s_us, 1e-9) * 1e-6) / hbm},
+            "linear prefill (projections, gates, one product per expert)": {"ms": r["pre_ops"]["linear"],
+                                                                            "of_measured_tensor": lin_flops / (r["pre_ops"]["linear"] * 1e-3) / tens},
+            "moe_linear decode (grouped, picked experts' weights once)": {"us": m_us, "experts_picked_all_layers": r["picked"], "of_measured_hbm":
+                                                                          r["picked"] * expert_w * 2 / (max(m_us, 1e-9) * 1e-6) / hbm},
+            "linear decode (tcgen05 projections)": {"us": g_us, "of_measured_hbm": (dense_w + head_w) * 2 / (max(g_us, 1e-9) * 1e-6) / hbm},
+        }
+        results.append(common(f"noganex-w{width}", raw, r, kernels, {"experts": moes[0]["router"]["experts"], "top": top}))
+        # ---------------------------------------------------------------- Dubesun, the partner
+        raw = dubesun_config(f"dubesun-w{width}")
+        names = ["linear", "embed_add_pos", "rmsnorm_rows", "causal_conv", "heads_prepare", "paged_attn", "diff_combine", "group_rmsnorm_gate",
+                 "moe_route", "moe_gather_rows", "moe_linear", "ff_clamped_gate", "moe_combine_add"]
+        r = _stream_family_measure(raw, dubesun_modeling.DubesunConfig(raw), names, PB, PL, DB, DL, K, Wm, timed, lib)
+        shapes = dubesun_modeling.tensor_shapes(raw)
+        attn_flops, attn_row = 0, 0
+        for layer in raw["layers"]:
+            m = layer["mixer"]
+            maps = 2 if layer["type"] == "attention" else 1
+            attn_flops += PB * (PL * (PL + 1) // 2) * m["heads"] * maps * (m["dim"] + m["vdim"]) * 2
+            attn_row += m["kv_heads"] * (maps * m["dim"] + m["vdim"])
+        f = raw["layers"][0]["mlp"]
+        expert_w, top, L = 3 * width * f["expert"]["ff"], f["router"]["top"], len(raw["layers"])
+        proj_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1]
+                     if n.split(".")[-1] in ("q", "k", "v", "g", "o", "router") and ".mlp.e" not in n)
+        head_w = shapes["head"][0] * shapes["head"][1]
+        lin_flops = 2 * PB * PL * (proj_w + L * top * expert_w) + 2 * PB * head_w
+        a_us, m_us, g_us = us(r["dec_k"], "paged_heads_attn"), r["dec_k"].get("moe_linear_mma_kernel", 0.0), r["dec_k"].get("gemm_f16_kernel", 0.0)
+        kernels = {
+            "paged_attn prefill": {"ms": r["pre_ops"]["paged_attn"], "tflops": attn_flops / r["pre_ops"]["paged_attn"] / 1e9,
+                                   "of_measured_tensor": attn_flops / (r["pre_ops"]["paged_attn"] * 1e-3) / tens},
+            "paged_attn decode": {"us": a_us, "of_measured_hbm": DB * ctx * attn_row * 2 / (max(a_us, 1e-9) * 1e-6) / hbm},
+            "linear prefill (projections + one product per expert)": {"ms": r["pre_ops"]["linear"],
+                                                                      "of_measured_tensor": lin_flops / (r["pre_ops"]["linear"] * 1e-3) / tens},
+            "moe_linear decode (grouped, picked experts' weights once)": {"us": m_us, "experts_picked_all_layers": r["picked"], "of_measured_hbm":
+                                                                          r["picked"] * expert_w * 2 / (max(m_us, 1e-9) * 1e-6) / hbm},
+            "linear decode (tcgen05 projections)": {"us": g_us, "of_measured_hbm": (proj_w + head_w) * 2 / (max(g_us, 1e-9) * 1e-6) / hbm},
+        }
+        results.append(common(f"dubesun-w{width}", raw, r, kernels, {"experts": f["router"]["experts"], "top": top}))
+    print(json.dumps({"metric": "noganex_compare", "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": Wm, "data": "synthetic",
+                      "config": {"prefill": [PB, PL], "decode": [DB, DL], "l2": "flushed between timed calls"},
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk.get("source")}, "models": results}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1090,6 +1279,8 @@ def main():
                     help="Fetotar beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     ap.add_argument("--dubesun-compare", action="store_true",
                     help="Dubesun beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
+    ap.add_argument("--noganex-compare", action="store_true",
+                    help="Noganex beside Dubesun at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -1097,6 +1288,8 @@ def main():
         return run_hybrid_compare(args)
     if args.dubesun_compare:
         return run_dubesun_compare(args)
+    if args.noganex_compare:
+        return run_noganex_compare(args)
     workload = args.workload or DEFAULT_WORKLOAD
     if workload in MIXED_WORKLOADS:
         if args.impl == "reference":

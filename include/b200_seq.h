@@ -140,7 +140,9 @@ int b200_seq_qk_rot_prepare(const float* src, int64_t ld, int col_q, int col_k, 
 int b200_seq_talk_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids,
                        const float* talk, float* out, int64_t T, int H, int G, int d, int dv, int chunk, int window, float scale, int page,
-                       void* stream);
+                       float* partial, int nsplit, void* stream);
+/* blocks to split each query tile's keys over for this step (0: plain kernel, 1: no split) and the fp32 workspace for `partial` */
+int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G, int d, int dv, int64_t* workspace_floats);
 
 #ifdef __cplusplus
 }

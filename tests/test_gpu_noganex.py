@@ -366,31 +366,36 @@ def _sharp(config, factor=4.0):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prompt_portions_and_decoding_agree_with_reference(tmp_path, dtype):
+    # bfloat16: a pick that flips on a near tie would stay in the recurrent memory for many tokens, so no row after it could be
+    # compared; there every expert is picked (the weights still come from the scores) and the picks themselves are tested per row
+    # in test_routed_experts_with_shared_match_reference
     cfg = _sharp(orc.random_config(order=("delta", "attention", "delta", "attention", "attention"), weights_of=(None, None, 0, None, 1),
-                                   mlp=("moe", "dense", "moe", None, "dense")), 4.0 if dtype == torch.float32 else 2.0)
+                                   mlp=("moe", "dense", "moe", None, "dense"), **({} if dtype == torch.float32 else {"experts": 3, "top": 3})),
+                 4.0 if dtype == torch.float32 else 2.0)
     sd = orc.random_state_dict(cfg, seed=11)
     model = _model(tmp_path, cfg, sd, dtype)
     toks = _tokens(2, 75, cfg["vocab"])
     ref = orc.forward(cfg, sd, toks)
     tol = TOL32 if dtype == torch.float32 else TOL16
     sure = _decided(cfg, sd, toks) if dtype == torch.bfloat16 else torch.ones(75, dtype=torch.bool)
-    assert int(sure.sum()) > 40
+    assert bool(sure.all())
     whole = _run_cut(model, toks, [75])
     assert _rel(whole[sure], ref[sure]) < tol
     # the mechanisms are live in this configuration: a reference with a chunk one token longer, without the shared tensors'
     # separate state, with another router scale or logit scale, or with the correction ignored is far outside the tolerance
-    def changed(edit, state=None):
-        c2, s2 = copy.deepcopy(cfg), dict(state or sd)
-        edit(c2, s2)
-        return _rel(orc.forward(c2, s2, toks), ref)
-    assert changed(lambda c, s: c["layers"][1]["mixer"]["mask"].update(size=25)) > 20 * TOL32
-    assert changed(lambda c, s: c["layers"][1]["mixer"]["rot"].update(dims=6)) > 20 * TOL32
-    assert changed(lambda c, s: c["layers"][1]["mixer"]["rot"].pop("scaling")) > 20 * TOL32
-    assert changed(lambda c, s: c["layers"][0]["mlp"]["router"].update(scale=1.4)) > 20 * TOL32
-    assert changed(lambda c, s: c.update(logit_scale=0.55)) > 20 * TOL32
-    assert changed(lambda c, s: s.update({"l0.mlp.correction": torch.zeros_like(s["l0.mlp.correction"])})) > 20 * TOL32
-    assert changed(lambda c, s: s.update({"l1.mix.talk": torch.eye(s["l1.mix.talk"].shape[0])})) > 20 * TOL32
-    assert changed(lambda c, s: s.update({"l0.rg1.b": s["l0.rg1.b"] + 1.0})) > 20 * TOL32
+    if dtype == torch.float32:
+        def changed(edit, state=None):
+            c2, s2 = copy.deepcopy(cfg), dict(state or sd)
+            edit(c2, s2)
+            return _rel(orc.forward(c2, s2, toks), ref)
+        assert changed(lambda c, s: c["layers"][1]["mixer"]["mask"].update(size=25)) > 20 * TOL32
+        assert changed(lambda c, s: c["layers"][1]["mixer"]["rot"].update(dims=6)) > 20 * TOL32
+        assert changed(lambda c, s: c["layers"][1]["mixer"]["rot"].pop("scaling")) > 20 * TOL32
+        assert changed(lambda c, s: c["layers"][0]["mlp"]["router"].update(scale=1.4)) > 20 * TOL32
+        assert changed(lambda c, s: c.update(logit_scale=0.55)) > 20 * TOL32
+        assert changed(lambda c, s: s.update({"l0.mlp.correction": torch.zeros_like(s["l0.mlp.correction"])})) > 20 * TOL32
+        assert changed(lambda c, s: s.update({"l1.mix.talk": torch.eye(s["l1.mix.talk"].shape[0])})) > 20 * TOL32
+        assert changed(lambda c, s: s.update({"l0.rg1.b": s["l0.rg1.b"] + 1.0})) > 20 * TOL32
     for cuts in ([], [40], [2, 2, 2, 19, 3, 16, 17, 2], [16, 16, 16, 16], [24, 24, 24], [23, 2, 23, 2], [1, 20, 22, 31]):
         got = _run_cut(model, toks, cuts)
         assert _rel(got[sure], ref[sure]) < tol, cuts
@@ -404,12 +409,12 @@ def test_tensor_core_shapes_through_the_engine(tmp_path):
     """bfloat16 with head sizes in 16s: prompts, portions and decoded tokens take the tensor-core attention kernel; a step mixes
     a long portion (several query tiles) with single tokens"""
     cfg = _sharp(orc.random_config(width=64, order=("attention", "delta", "attention"), weights_of=(None, None, 0), heads=(8, 4), kv_heads=(2, 2),
-                                   dim=(32, 16), vdim=(16, 32), rot_dims=16, chunk=60, mlp=("dense", "moe", "dense")), 2.0)
+                                   dim=(32, 16), vdim=(16, 32), rot_dims=16, chunk=60, mlp=("dense", "moe", "dense"), experts=4, top=4), 2.0)
     sd = orc.random_state_dict(cfg, seed=12)
     model = _model(tmp_path, cfg, sd, torch.bfloat16)
     toks = _tokens(3, 150, cfg["vocab"])
     ref, sure = orc.forward(cfg, sd, toks), _decided(cfg, sd, toks)
-    assert int(sure.sum()) > 100
+    assert bool(sure.all())   # every expert is picked: see test_prompt_portions_and_decoding_agree_with_reference
     for cuts in ([150], [100, 2, 40], [1, 70, 33], [5]):
         assert _rel(_run_cut(model, toks, cuts)[sure], ref[sure]) < TOL16, cuts
     other = _tokens(4, 90, cfg["vocab"])

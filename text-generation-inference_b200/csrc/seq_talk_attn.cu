@@ -164,6 +164,312 @@ __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form for bfloat16 caches.  One block per (sequence, tile of QT query tokens): its R = QT * heads rows are ordered
+// (key head group, token, query head of the group), so that the 16 rows of a warp share one group and read that group's key and
+// value columns; R / 16 warps.  Per tile of KT keys (16-byte cp.async, two stages; a tile holds the keys and values of ALL
+// groups): every warp computes the raw scores of its rows with m16n8k16 products and leaves them, scaled, in shared memory in
+// fp32; after a barrier each thread gathers, for the (row, key) elements of its own accumulator fragment, the scores of all
+// heads of the same token and mixes them with FFMAs in fp32 (the mix is the one step that crosses warps); mask, fp32 online
+// soft-max and O += P V follow per warp with P in registers.  gridDim.z > 1 deals the tile's keys out in runs whose partial
+// (output, max, sum) talk_attn_merge_kernel joins.  Needs dim % 16 == 0, vdim % 16 == 0, vdim <= 128 and QT * (heads / kv_heads)
+// a multiple of 16; everything else takes the plain kernel.
+// ------------------------------------------------------------------------------------------------------------------------
+constexpr int kTalkPad = 8;
+
+// which (sequence, tile of QT of its rows) block `tile` has; b == B: none
+__device__ __forceinline__ void talk_find_tile(const int32_t* cu_q, int B, int QT, int tile, int& b, int& row0, int& ntok) {
+  for (b = 0; b < B; ++b) {
+    const int n = cu_q[b + 1] - cu_q[b];
+    const int nt = (n + QT - 1) / QT;
+    if (tile < nt) {
+      row0 = cu_q[b] + tile * QT;
+      ntok = min(QT, cu_q[b + 1] - row0);
+      return;
+    }
+    tile -= nt;
+  }
+}
+
+template <int NDV, int KT>  // NDV = vdim / 8 output n-tiles per warp, KT keys per tile
+__global__ void __launch_bounds__(512) talk_attn_mma_kernel(
+    const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
+    int64_t bt_stride, const int32_t* __restrict__ cu_q, int B, const int64_t* __restrict__ position_ids, const float* __restrict__ talk,
+    float* __restrict__ out, int H, int G, int d, int QT, int chunk, int window, float scale, int page, float* __restrict__ partial) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int dv = NDV * 8, STAGES = 2, SP = KT + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int rep = H / G, R = QT * H, rows_g = QT * rep;
+  const int KD = G * d, KP = KD + kTalkPad, VD = G * dv, VP = VD + kTalkPad, DP = d + kTalkPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [R][DP]
+  __nv_bfloat16* Ks = Qs + R * DP;                                   // [STAGES][KT][KP]
+  __nv_bfloat16* Vs = Ks + STAGES * KT * KP;                         // [STAGES][KT][VP]
+  float* Ss = reinterpret_cast<float*>(Vs + STAGES * KT * VP);       // [R][SP] scaled raw scores of the tile
+  float* Ts = Ss + R * SP;                                           // [H][H]
+  int b, row0 = 0, ntok = 0;
+  talk_find_tile(cu_q, B, QT, blockIdx.x, b, row0, ntok);
+  if (b >= B) return;  // block-uniform: no barrier has been met yet
+  const int nthreads = blockDim.x;
+  const int p0 = (int)position_ids[row0], p_last = p0 + ntok - 1;
+  const int j_first = first_visible(p0, chunk, window);
+  const int n_ktiles = (p_last - j_first + KT) / KT;
+  const int per_split = (n_ktiles + gridDim.z - 1) / gridDim.z;
+  const int j_start = j_first + (int)blockIdx.z * per_split * KT;
+  const int j_end = min(p_last, j_start + per_split * KT - 1);   // last key of this block's run
+  const int w = warp_id(), lane = lane_id();
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  for (int r = w; r < R; r += nthreads / 32) {
+    const int c = r / rows_g, rr = r % rows_g, tok = rr / rep, hh = rr % rep;
+    const float* src = q + ((int64_t)(row0 + tok) * H + c * rep + hh) * d;
+    const bool live = tok < ntok;
+    for (int i = lane; i < d; i += 32) Qs[r * DP + i] = __float2bfloat16_rn(live ? src[i] : 0.f);
+  }
+  if (talk)
+    for (int i = threadIdx.x; i < H * H; i += nthreads) Ts[i] = talk[i];
+  const int kchunks = KD / 8, vchunks = VD / 8;
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+  auto load_tile = [&](int stage, int j0) {
+    __nv_bfloat16* kd = Ks + stage * KT * KP;
+    __nv_bfloat16* vd = Vs + stage * KT * VP;
+    for (int row = threadIdx.x >> 3; row < KT; row += nthreads >> 3) {
+      const int j = j0 + row;
+      __nv_bfloat16* krow = kd + row * KP;
+      __nv_bfloat16* vrow = vd + row * VP;
+      if (j <= j_end) {
+        const int64_t blk = table[page_shift >= 0 ? j >> page_shift : j / page];
+        const int tk = page_shift >= 0 ? j & (page - 1) : j % page;
+        const __nv_bfloat16* src = cache + (blk * page + tk) * RW;
+        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, src + k_off + ch * 8, true);
+        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, src + v_off + ch * 8, true);
+      } else {
+        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(krow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) *reinterpret_cast<uint4*>(vrow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: p = 0
+      }
+    }
+    cp_async_commit();
+  };
+  // this thread's two accumulator rows
+  const int cq = (lane & 3) * 2;
+  const int c_w = (w * 16) / rows_g;   // the warp's key / value head group
+  int p_row[2], lo_row[2], h_row[2], tok_row[2];
+  bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = w * 16 + (lane >> 2) + i * 8, rr = r % rows_g;
+    tok_row[i] = rr / rep;
+    valid[i] = tok_row[i] < ntok;
+    p_row[i] = valid[i] ? p0 + tok_row[i] : p0;
+    lo_row[i] = first_visible(p_row[i], chunk, window);
+    h_row[i] = c_w * rep + rr % rep;
+  }
+  const bool warp_active = ((w * 16) % rows_g) / rep < ntok;  // rows of a warp ascend in token: its first row decides
+  const int lo_last = first_visible(p_last, chunk, window);
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[NDV][4];
+#pragma unroll
+  for (int i = 0; i < NDV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+  const int lm = lane >> 3, lr = lane & 7;
+  const uint32_t a_lane = qs_addr + (uint32_t)(((w * 16 + (lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
+  if (j_start <= j_end) load_tile(0, j_start);
+  else cp_async_commit();
+  int stage = 0;
+  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage ^= 1) {
+    {
+      const int jn = j0 + KT;
+      if (jn <= j_end) load_tile(stage ^ 1, jn);
+      else cp_async_commit();
+      cp_async_wait<1>();
+    }
+    __syncthreads();  // the tile (and, first time round, Qs / Ts) is in shared memory; the previous tile's scores are consumed
+    float s[KT / 8][4];
+#pragma unroll
+    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    if (warp_active) {
+      const uint32_t b_lane = ks_addr + (uint32_t)(((stage * KT + (lm >> 1) * 8 + lr) * KP + c_w * d + (lm & 1) * 8) * 2);
+      for (int kk = 0; kk < d; kk += 16) {
+        uint32_t a[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
+#pragma unroll
+        for (int kg = 0; kg < KT / 16; ++kg) {
+          uint32_t bb[4];
+          ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)((kg * 16 * KP + kk) * 2));
+          mma_m16n8k16_bf16f32(s[2 * kg], a, bb[0], bb[1]);
+          mma_m16n8k16_bf16f32(s[2 * kg + 1], a, bb[2], bb[3]);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] *= scale;
+    }
+    if (talk) {
+      // all heads' scores of the tile meet in shared memory; every thread then mixes the elements of its own fragment
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float* dst = Ss + (w * 16 + (lane >> 2) + i * 8) * SP + cq;
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(s[nt][i * 2], s[nt][i * 2 + 1]);
+      }
+      __syncthreads();
+      if (warp_active) {
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int g = 0; g < H; ++g) {
+          const int base = (g / rep) * rows_g + g % rep;
+          const float t0 = Ts[h_row[0] * H + g], t1 = Ts[h_row[1] * H + g];
+          const float* ra = Ss + (base + tok_row[0] * rep) * SP + cq;
+          const float* rb = Ss + (base + tok_row[1] * rep) * SP + cq;
+#pragma unroll
+          for (int nt = 0; nt < KT / 8; ++nt) {
+            const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8), vb = *reinterpret_cast<const float2*>(rb + nt * 8);
+            s[nt][0] = fmaf(t0, va.x, s[nt][0]);
+            s[nt][1] = fmaf(t0, va.y, s[nt][1]);
+            s[nt][2] = fmaf(t1, vb.x, s[nt][2]);
+            s[nt][3] = fmaf(t1, vb.y, s[nt][3]);
+          }
+        }
+      }
+    }
+    if (warp_active) {
+      float mx[2] = {-INFINITY, -INFINITY};
+      if (j0 + KT - 1 <= min(j_end, p0) && j0 >= lo_last) {
+        // an interior tile: every key is visible to every row
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
+            if (j > p_row[i] || j < lo_row[i] || j > j_end) s[nt][e] = -INFINITY;
+            mx[i] = fmaxf(mx[i], s[nt][e]);
+          }
+      }
+      float m_use[2], corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        const float m_new = fmaxf(m_run[i], mx[i]);
+        m_use[i] = m_new == -INFINITY ? 0.f : m_new;  // a row that has met no visible key yet
+        corr[i] = expf(m_run[i] - m_use[i]);
+        m_run[i] = m_new;
+      }
+      uint32_t pa[KT / 16][4];
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(expf(s[nt][0] - m_use[0]), expf(s[nt][1] - m_use[0]));
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(expf(s[nt][2] - m_use[1]), expf(s[nt][3] - m_use[1]));
+        // the sums use the rounded probabilities: numerator and denominator see the same weights
+        sum[0] += __low2float(lo) + __high2float(lo);
+        sum[1] += __low2float(hi) + __high2float(hi);
+        pa[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&lo);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+        l_run[i] = l_run[i] * corr[i] + sum[i];
+      }
+#pragma unroll
+      for (int i = 0; i < NDV; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      const uint32_t v_lane = vs_addr + (uint32_t)(((stage * KT + (lm & 1) * 8 + lr) * VP + c_w * dv + (lm >> 1) * 8) * 2);
+#pragma unroll
+      for (int kg = 0; kg < KT / 16; ++kg) {
+#pragma unroll
+        for (int nt = 0; nt < NDV; nt += 2) {
+          uint32_t bb[4];
+          ldmatrix_x4_trans(bb[0], bb[1], bb[2], bb[3], v_lane + (uint32_t)((kg * 16 * VP + nt * 8) * 2));
+          mma_m16n8k16_bf16f32(o[nt], pa[kg], bb[0], bb[1]);
+          mma_m16n8k16_bf16f32(o[nt + 1], pa[kg], bb[2], bb[3]);
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with this stage (and with the scores) before the next iteration overwrites them
+  }
+  if (gridDim.z > 1) {
+    // partial [tile][split][R rows][dv + 2]: unnormalised output, then the running max and sum
+    float* base = partial + (((int64_t)blockIdx.x * gridDim.z + blockIdx.z) * R) * (dv + 2);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!valid[i]) continue;
+      float* dst = base + (int64_t)(w * 16 + (lane >> 2) + i * 8) * (dv + 2);
+#pragma unroll
+      for (int nt = 0; nt < NDV; ++nt) {
+        dst[nt * 8 + cq] = o[nt][i * 2];
+        dst[nt * 8 + cq + 1] = o[nt][i * 2 + 1];
+      }
+      if ((lane & 3) == 0) {
+        dst[dv] = m_run[i];
+        dst[dv + 1] = l_run[i];
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!valid[i]) continue;
+    float* dst = out + ((int64_t)(row0 + tok_row[i]) * H + h_row[i]) * dv;
+    const float inv = 1.f / l_run[i];
+#pragma unroll
+    for (int nt = 0; nt < NDV; ++nt) {
+      dst[nt * 8 + cq] = o[nt][i * 2] * inv;
+      dst[nt * 8 + cq + 1] = o[nt][i * 2 + 1] * inv;
+    }
+  }
+}
+
+// out[row] = sum_z e^(m_z - M) O_z / sum_z e^(m_z - M) l_z over the key runs of talk_attn_mma_kernel; one block per query tile, one
+// warp per row
+__global__ void __launch_bounds__(256) talk_attn_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, const int32_t* __restrict__ cu_q,
+                                                             int B, int H, int G, int QT, int dv, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int b, row0 = 0, ntok = 0;
+  talk_find_tile(cu_q, B, QT, blockIdx.x, b, row0, ntok);
+  if (b >= B) return;
+  const int rep = H / G, R = QT * H, rows_g = QT * rep, lane = lane_id();
+  constexpr int kMaxSplit = 8;
+  for (int r = warp_id(); r < R; r += 8) {
+    const int c = r / rows_g, rr = r % rows_g, tok = rr / rep;
+    if (tok >= ntok) continue;
+    const float* base = partial + (((int64_t)blockIdx.x * nsplit) * R + r) * (dv + 2);
+    const int64_t zs = (int64_t)R * (dv + 2);
+    float M = -INFINITY, wz[kMaxSplit];
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = z < nsplit ? base[z * zs + dv] : -INFINITY;
+      M = fmaxf(M, wz[z]);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = wz[z] > -INFINITY ? expf(wz[z] - M) : 0.f;  // an empty run carries no weight
+      if (z < nsplit) den += wz[z] * base[z * zs + dv + 1];
+    }
+    const float inv = 1.f / den;
+    float* dst = out + ((int64_t)(row0 + tok) * H + c * rep + rr % rep) * dv;
+    for (int col = lane; col < dv; col += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int z = 0; z < kMaxSplit; ++z)
+        if (z < nsplit) acc = fmaf(wz[z], base[z * zs + col], acc);
+      dst[col] = acc * inv;
+    }
+  }
+}
+
 }  // namespace seq
 }  // namespace b200
 
@@ -203,19 +509,90 @@ static int launch_talk_plain(const float* q, const void* cache, int64_t RW, int 
   return B200_OK;
 }
 
-// q fp32 [T, H, d]; cache rows as above; talk fp32 [H, H] or NULL (no mix); chunk / window <= 0: none -> out fp32 [T, H, dv]
+// How the tensor-core kernel would run a step: tokens per query tile (0: the shape takes the plain kernel), keys per tile, shared memory
+struct TalkPlan { int QT, KT; size_t smem; };
+
+static TalkPlan talk_mma_plan(int dt, int64_t T, int B, int H, int G, int d, int dv, bool has_talk) {
+  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_ATTN_MMA"); return !(e && e[0] == '0'); }();
+  TalkPlan p{0, 0, 0};
+  if (!use_mma || dt != B200_DT_BF16 || G <= 0 || H % G != 0 || d % 16 != 0 || dv % 16 != 0 || dv > 128 || (dv / 8 != 2 && dv / 8 != 4 && dv / 8 != 8 && dv / 8 != 16))
+    return p;
+  const int rep = H / G;
+  int g16 = 16, x = rep;
+  while (x % 2 == 0 && g16 > 1) { x /= 2; g16 /= 2; }   // g16 = 16 / gcd(16, rep)
+  int QT = g16;
+  if ((int64_t)QT * H > 256) return p;
+  if (T > 2 * (int64_t)B)                                // prompts and portions: larger tiles share each key tile among more rows
+    while ((int64_t)QT * 2 * H <= 128) QT *= 2;
+  const int R = QT * H;
+  for (int KT : {64, 16}) {
+    const size_t smem = ((size_t)R * (d + kTalkPad) + (size_t)2 * KT * (G * d + kTalkPad) + (size_t)2 * KT * (G * dv + kTalkPad)) * 2 +
+                        ((size_t)R * (KT + 8) + (has_talk ? (size_t)H * H : 0)) * 4;
+    if (smem <= 200 * 1024) { p.QT = QT; p.KT = KT; p.smem = smem; return p; }
+  }
+  return p;
+}
+
+// Over how many blocks the tensor-core kernel should split each query tile's keys in this step (1: no split; 0: the plain kernel runs)
+// and the fp32 workspace (`partial`) that takes
+extern "C" int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G, int d, int dv, int64_t* workspace_floats) {
+  if (workspace_floats) *workspace_floats = 0;
+  const TalkPlan p = talk_mma_plan(dt, T, B, H, G, d, dv, true);
+  if (p.QT == 0) return 0;
+  const int64_t tiles = (T + p.QT - 1) / p.QT + B;
+  const int64_t busy = (T + p.QT - 1) / p.QT > B ? (T + p.QT - 1) / p.QT : B;
+  int64_t n = (2 * 148) / (busy > 0 ? busy : 1);
+  n = n < 1 ? 1 : (n > 8 ? 8 : n);
+  if (n > 1 && workspace_floats) *workspace_floats = tiles * n * p.QT * H * (dv + 2);
+  return (int)n;
+}
+
+// q fp32 [T, H, d]; cache rows as above; talk fp32 [H, H] or NULL (no mix); chunk / window <= 0: none -> out fp32 [T, H, dv].
+// `partial` / nsplit: from b200_seq_talk_attn_splits (NULL / <= 1: no split).
 extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
                                   int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids,
                                   const float* talk, float* out, int64_t T, int H, int G, int d, int dv, int chunk, int window, float scale,
-                                  int page, void* stream) {
+                                  int page, float* partial, int nsplit, void* stream) {
   if (T == 0) return B200_OK;
   if (G <= 0 || H % G != 0 || d <= 0 || dv <= 0 || dv > 256) {
     b200_set_last_error("seq_talk_attn: need heads % kv_heads == 0 and 0 < vdim <= 256");
     return B200_ERR_ARG;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  (void)cu_q;
-  (void)B;
+  const TalkPlan plan = talk_mma_plan(dt, T, B, H, G, d, dv, talk != nullptr);
+  if (plan.QT > 0 && cu_q != nullptr && row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+    const int64_t tiles = (T + plan.QT - 1) / plan.QT + B;  // upper bound of sum_b ceil(n_b / QT); surplus blocks return at once
+    if (!partial || nsplit < 1) nsplit = 1;
+    if (nsplit > 8) nsplit = 8;
+    if (tiles <= 0x7fffffff) {
+      dim3 grid((unsigned)tiles, 1, (unsigned)nsplit);
+      const unsigned threads = (unsigned)(plan.QT * H / 16 * 32);
+#define TAM(N, KT)                                                                                                                       \
+  do {                                                                                                                                   \
+    static bool cfg = false;                                                                                                             \
+    if (!cfg) { cudaFuncSetAttribute(talk_attn_mma_kernel<N, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
+    B200_LAUNCH((talk_attn_mma_kernel<N, KT>), grid, dim3(threads), plan.smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
+                block_table, bt_stride, cu_q, B, position_ids, talk, out, H, G, d, plan.QT, chunk, window, scale, page, partial);        \
+  } while (0)
+#define TAM_KT(N)                 \
+  do {                            \
+    if (plan.KT == 64) TAM(N, 64); \
+    else TAM(N, 16);              \
+  } while (0)
+      switch (dv / 8) {
+        case 2: TAM_KT(2); break;
+        case 4: TAM_KT(4); break;
+        case 8: TAM_KT(8); break;
+        default: TAM_KT(16); break;
+      }
+#undef TAM_KT
+#undef TAM
+      if (nsplit > 1)
+        B200_LAUNCH(talk_attn_merge_kernel, dim3((unsigned)tiles), dim3(256), 0, st, (const float*)partial, out, cu_q, B, H, G, plan.QT, dv, nsplit);
+      b200_count_launches(nsplit > 1 ? 2 : 1);
+      return B200_OK;
+    }
+  }
 #define TALK(N)                                                                                                                              \
   B200_SEQ_DISPATCH(dt, E, return (launch_talk_plain<E, N>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, position_ids, \
                                                           talk, out, T, H, G, d, dv, chunk, window, scale, page, st)))

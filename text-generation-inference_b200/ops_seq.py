@@ -495,8 +495,12 @@ def talk_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, kv_head
     assert q.is_contiguous() and cache.is_contiguous() and q.dtype == torch.float32
     assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (H, H))
     out = torch.empty(T, H, vdim, dtype=torch.float32, device=q.device)
-    _lib.check_seq(_lib.load_seq().b200_seq_talk_attn(
+    lib = _lib.load_seq()
+    need = ctypes.c_int64(0)
+    nsplit = lib.b200_seq_talk_attn_splits(_dt(cache), T, step.B, H, kv_heads, d, vdim, ctypes.byref(need)) if _ATTN_SPLIT else 1
+    partial = torch.empty(need.value, dtype=torch.float32, device=q.device) if nsplit > 1 else None
+    _lib.check_seq(lib.b200_seq_talk_attn(
         _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
         _ptr(step.seq_of_token), _ptr(step.cu_q), step.B, _ptr(step.position_ids), _ptr(talk), _ptr(out), T, H, kv_heads, d, vdim, int(chunk),
-        int(window), float(scale), cache.shape[1], _stream()), "seq_talk_attn")
+        int(window), float(scale), cache.shape[1], _ptr(partial), nsplit, _stream()), "seq_talk_attn")
     return out

@@ -64,13 +64,32 @@ def dubesun_config(name: str) -> dict:
     return {"architecture": "Dubesun", "layers": layers, "max_positions": 2048, "norm": {"eps": 1e-5}, "vocab": 32000, "width": W}
 
 
+def noganex_config(name: str) -> dict:
+    """Three layers at the widths of the `dubesun-w*` / `neox-w*` partners: head-mixed attention (chunks of 2048, half of each head
+    rotated, YaRN) with a gated MLP, the gated delta rule with 16 routed experts (2 per token) and a shared expert, and a second
+    attention layer with routed experts: raw config.json of the Noganex family."""
+    W = {"noganex-w2048": 2048, "noganex-w4096": 4096}[name]
+    moe = {"kind": "moe", "expert": {"ff": W * 11 // 16}, "router": {"experts": 16, "top": 2, "scale": 2.5}, "shared": {"ff": W * 11 // 16}}
+    attn = {"dim": 128, "heads": W // 128, "kv_heads": W // 512, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 2048},
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}}}
+    delta = {"conv": 4, "dim": 128, "heads": W // 128, "kv_heads": W // 256, "vdim": 128}
+    layers = [
+        {"type": "attention", "mixer": dict(attn), "mlp": {"kind": "dense", "ff": W * 11 // 4}},
+        {"type": "delta", "mixer": dict(delta), "mlp": dict(moe)},
+        {"type": "attention", "mixer": dict(attn), "mlp": dict(moe)},
+    ]
+    return {"architecture": "Noganex", "layers": layers, "logit_scale": 1.0, "norm": {"eps": 1e-5}, "vocab": 32000, "width": W}
+
+
 class SyntheticHybridWeights:
-    """Seeded random tensors of a Fetotar or Dubesun configuration, generated on the device by name (the `get_tensor` side of
-    `Weights`)."""
+    """Seeded random tensors of a Fetotar, Dubesun or Noganex configuration, generated on the device by name (the `get_tensor` side
+    of `Weights`)."""
 
     def __init__(self, raw_config: dict, device, dtype, process_group, seed: int = 1234):
         if raw_config.get("architecture") == "Dubesun":
             from ..models.custom_modeling.dubesun_modeling import tensor_shapes
+        elif raw_config.get("architecture") == "Noganex":
+            from ..models.custom_modeling.noganex_modeling import tensor_shapes
         else:
             from ..models.custom_modeling.fetotar_modeling import tensor_shapes
         self.shapes, self.device, self.dtype, self.process_group, self.seed = tensor_shapes(raw_config), device, dtype, process_group, seed
@@ -80,7 +99,9 @@ class SyntheticHybridWeights:
         shape = self.shapes[name]
         gen = torch.Generator(device=self.device).manual_seed(self.seed * 1000003 + zlib.crc32(name.encode()))
         leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
-        if len(shape) == 2:
+        if leaf == "mix.talk":   # near the identity: every head mostly keeps its own scores
+            t = torch.eye(shape[0], device=self.device) + torch.empty(shape, device=self.device).normal_(0.0, 0.1 / shape[0] ** 0.5, generator=gen)
+        elif len(shape) == 2:
             std = 0.5 if leaf.endswith("conv") else 1.0 / (shape[1] ** 0.5)
             t = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen)
         elif leaf in ("mix.A_log", "mix.dt_bias"):
