@@ -316,18 +316,21 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
       if (warp_active) {
 #pragma unroll
         for (int nt = 0; nt < KT / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-        for (int g = 0; g < H; ++g) {
-          const int base = (g / rep) * rows_g + g % rep;
-          const float t0 = Ts[h_row[0] * H + g], t1 = Ts[h_row[1] * H + g];
-          const float* ra = Ss + (base + tok_row[0] * rep) * SP + cq;
-          const float* rb = Ss + (base + tok_row[1] * rep) * SP + cq;
+        // rows of tokens that the tile does not have (a decoding step fills one token of QT) are left at zero
 #pragma unroll
-          for (int nt = 0; nt < KT / 8; ++nt) {
-            const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8), vb = *reinterpret_cast<const float2*>(rb + nt * 8);
-            s[nt][0] = fmaf(t0, va.x, s[nt][0]);
-            s[nt][1] = fmaf(t0, va.y, s[nt][1]);
-            s[nt][2] = fmaf(t1, vb.x, s[nt][2]);
-            s[nt][3] = fmaf(t1, vb.y, s[nt][3]);
+        for (int i = 0; i < 2; ++i) {
+          if (!valid[i]) continue;
+          const float* trow = Ts + h_row[i] * H;
+          const float* srow = Ss + tok_row[i] * rep * SP + cq;
+          for (int g = 0; g < H; ++g) {
+            const float tg = trow[g];
+            const float* ra = srow + ((g / rep) * rows_g + g % rep) * SP;
+#pragma unroll
+            for (int nt = 0; nt < KT / 8; ++nt) {
+              const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8);
+              s[nt][i * 2] = fmaf(tg, va.x, s[nt][i * 2]);
+              s[nt][i * 2 + 1] = fmaf(tg, va.y, s[nt][i * 2 + 1]);
+            }
           }
         }
       }
@@ -430,8 +433,7 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
   }
 }
 
-// out[row] = sum_z e^(m_z - M) O_z / sum_z e^(m_z - M) l_z over the key runs of talk_attn_mma_kernel; one block per query tile, one
-// warp per row
+// out[row] = sum_z e^(m_z - M) O_z / sum_z e^(m_z - M) l_z over the key runs of talk_attn_mma_kernel; one warp per row, blocks (query tile, 8 rows)
 __global__ void __launch_bounds__(256) talk_attn_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, const int32_t* __restrict__ cu_q,
                                                              int B, int H, int G, int QT, int dv, int nsplit) {
   pdl_launch_dependents();
@@ -441,7 +443,7 @@ __global__ void __launch_bounds__(256) talk_attn_merge_kernel(const float* __res
   if (b >= B) return;
   const int rep = H / G, R = QT * H, rows_g = QT * rep, lane = lane_id();
   constexpr int kMaxSplit = 8;
-  for (int r = warp_id(); r < R; r += 8) {
+  for (int r = blockIdx.y * 8 + warp_id(); r < R; r += 8 * gridDim.y) {
     const int c = r / rows_g, rr = r % rows_g, tok = rr / rep;
     if (tok >= ntok) continue;
     const float* base = partial + (((int64_t)blockIdx.x * nsplit) * R + r) * (dv + 2);
@@ -525,7 +527,7 @@ static TalkPlan talk_mma_plan(int dt, int64_t T, int B, int H, int G, int d, int
   if (T > 2 * (int64_t)B)                                // prompts and portions: larger tiles share each key tile among more rows
     while ((int64_t)QT * 2 * H <= 128) QT *= 2;
   const int R = QT * H;
-  for (int KT : {64, 16}) {
+  for (int KT : {64, 32, 16}) {
     const size_t smem = ((size_t)R * (d + kTalkPad) + (size_t)2 * KT * (G * d + kTalkPad) + (size_t)2 * KT * (G * dv + kTalkPad)) * 2 +
                         ((size_t)R * (KT + 8) + (has_talk ? (size_t)H * H : 0)) * 4;
     if (smem <= 200 * 1024) { p.QT = QT; p.KT = KT; p.smem = smem; return p; }
@@ -541,7 +543,10 @@ extern "C" int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G,
   if (p.QT == 0) return 0;
   const int64_t tiles = (T + p.QT - 1) / p.QT + B;
   const int64_t busy = (T + p.QT - 1) / p.QT > B ? (T + p.QT - 1) / p.QT : B;
-  int64_t n = (2 * 148) / (busy > 0 ? busy : 1);
+  // as many runs as keep all blocks resident at once (shared memory decides how many share an SM)
+  int64_t per_sm = (int64_t)(220 * 1024) / (int64_t)(p.smem + 1024);
+  per_sm = per_sm < 1 ? 1 : per_sm;
+  int64_t n = (148 * per_sm) / (busy > 0 ? busy : 1);
   n = n < 1 ? 1 : (n > 8 ? 8 : n);
   if (n > 1 && workspace_floats) *workspace_floats = tiles * n * p.QT * H * (dv + 2);
   return (int)n;
@@ -577,6 +582,7 @@ extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int
 #define TAM_KT(N)                 \
   do {                            \
     if (plan.KT == 64) TAM(N, 64); \
+    else if (plan.KT == 32) TAM(N, 32); \
     else TAM(N, 16);              \
   } while (0)
       switch (dv / 8) {
@@ -588,7 +594,7 @@ extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int
 #undef TAM_KT
 #undef TAM
       if (nsplit > 1)
-        B200_LAUNCH(talk_attn_merge_kernel, dim3((unsigned)tiles), dim3(256), 0, st, (const float*)partial, out, cu_q, B, H, G, plan.QT, dv, nsplit);
+        B200_LAUNCH(talk_attn_merge_kernel, dim3((unsigned)tiles, (unsigned)((plan.QT * H + 7) / 8)), dim3(256), 0, st, (const float*)partial, out, cu_q, B, H, G, plan.QT, dv, nsplit);
       b200_count_launches(nsplit > 1 ? 2 : 1);
       return B200_OK;
     }
