@@ -167,11 +167,13 @@ __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
 // ------------------------------------------------------------------------------------------------------------------------
 // Tensor-core form for bfloat16 caches.  One block per (sequence, tile of QT query tokens): its R = QT * heads rows are ordered
 // (key head group, token, query head of the group), so that the 16 rows of a warp share one group and read that group's key and
-// value columns; R / 16 warps.  Per tile of KT keys (16-byte cp.async, two stages; a tile holds the keys and values of ALL
-// groups): every warp computes the raw scores of its rows with m16n8k16 products and leaves them, scaled, in shared memory in
-// fp32; after a barrier each thread gathers, for the (row, key) elements of its own accumulator fragment, the scores of all
-// heads of the same token and mixes them with FFMAs in fp32 (the mix is the one step that crosses warps); mask, fp32 online
-// soft-max and O += P V follow per warp with P in registers.  gridDim.z > 1 deals the tile's keys out in runs whose partial
+// value columns; R / 16 warps.  Per tile of KT keys (16-byte cp.async; a tile holds the keys and values of ALL groups): every
+// warp computes the raw scores of its rows with m16n8k16 products and leaves them, scaled, in shared memory in fp32; after a
+// barrier each thread gathers, for the (row, key) elements of its own accumulator fragment, the scores of all heads of the same
+// token and mixes them with FFMAs in fp32 (the mix is the one step that crosses warps); mask, fp32 online soft-max and
+// O += P V follow per warp with P in registers.  There is ONE key buffer and ONE value buffer, so that two blocks share an SM at
+// the sizes of a real model: the next tile's keys are fetched as soon as the scores are done (while the mix, the soft-max and
+// P V run), its values when P V is done (while the next scores run).  gridDim.z > 1 deals the tile's keys out in runs whose partial
 // (output, max, sum) talk_attn_merge_kernel joins.  Needs dim % 16 == 0, vdim % 16 == 0, vdim <= 128 and QT * (heads / kv_heads)
 // a multiple of 16; everything else takes the plain kernel.
 // ------------------------------------------------------------------------------------------------------------------------
@@ -198,15 +200,14 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
     float* __restrict__ out, int H, int G, int d, int QT, int chunk, int window, float scale, int page, float* __restrict__ partial) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int dv = NDV * 8, STAGES = 2, SP = KT + 8;
+  constexpr int dv = NDV * 8, SP = KT + 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int rep = H / G, R = QT * H, rows_g = QT * rep;
   const int KD = G * d, KP = KD + kTalkPad, VD = G * dv, VP = VD + kTalkPad, DP = d + kTalkPad;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [R][DP]
-  __nv_bfloat16* Ks = Qs + R * DP;                                   // [STAGES][KT][KP]
-  __nv_bfloat16* Vs = Ks + STAGES * KT * KP;                         // [STAGES][KT][VP]
-  float* Ss = reinterpret_cast<float*>(Vs + STAGES * KT * VP);       // [R][SP] scaled raw scores of the tile
-  float* Ts = Ss + R * SP;                                           // [H][H]
+  __nv_bfloat16* Ks = Qs + R * DP;                                   // [KT][KP]
+  __nv_bfloat16* Vs = Ks + KT * KP;                                  // [KT][VP]
+  float* Ss = reinterpret_cast<float*>(Vs + KT * VP);                // [R][SP] scaled raw scores of the tile
   int b, row0 = 0, ntok = 0;
   talk_find_tile(cu_q, B, QT, blockIdx.x, b, row0, ntok);
   if (b >= B) return;  // block-uniform: no barrier has been met yet
@@ -225,26 +226,20 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
     const bool live = tok < ntok;
     for (int i = lane; i < d; i += 32) Qs[r * DP + i] = __float2bfloat16_rn(live ? src[i] : 0.f);
   }
-  if (talk)
-    for (int i = threadIdx.x; i < H * H; i += nthreads) Ts[i] = talk[i];
   const int kchunks = KD / 8, vchunks = VD / 8;
   const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
-  auto load_tile = [&](int stage, int j0) {
-    __nv_bfloat16* kd = Ks + stage * KT * KP;
-    __nv_bfloat16* vd = Vs + stage * KT * VP;
+  // one block-table lookup per thread and row, then the row's 16-byte pieces go round eight threads
+  auto load_rows = [&](__nv_bfloat16* dst, int ld, int off, int chunks, int j0) {
     for (int row = threadIdx.x >> 3; row < KT; row += nthreads >> 3) {
       const int j = j0 + row;
-      __nv_bfloat16* krow = kd + row * KP;
-      __nv_bfloat16* vrow = vd + row * VP;
+      __nv_bfloat16* drow = dst + row * ld;
       if (j <= j_end) {
         const int64_t blk = table[page_shift >= 0 ? j >> page_shift : j / page];
         const int tk = page_shift >= 0 ? j & (page - 1) : j % page;
-        const __nv_bfloat16* src = cache + (blk * page + tk) * RW;
-        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, src + k_off + ch * 8, true);
-        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, src + v_off + ch * 8, true);
+        const __nv_bfloat16* src = cache + (blk * page + tk) * RW + off;
+        for (int ch = threadIdx.x & 7; ch < chunks; ch += 8) cp_async_16(drow + ch * 8, src + ch * 8, true);
       } else {
-        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(krow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
-        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) *reinterpret_cast<uint4*>(vrow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: p = 0
+        for (int ch = threadIdx.x & 7; ch < chunks; ch += 8) *reinterpret_cast<uint4*>(drow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: p = 0
       }
     }
     cp_async_commit();
@@ -272,22 +267,16 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
   const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
   const int lm = lane >> 3, lr = lane & 7;
   const uint32_t a_lane = qs_addr + (uint32_t)(((w * 16 + (lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
-  if (j_start <= j_end) load_tile(0, j_start);
-  else cp_async_commit();
-  int stage = 0;
-  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage ^= 1) {
-    {
-      const int jn = j0 + KT;
-      if (jn <= j_end) load_tile(stage ^ 1, jn);
-      else cp_async_commit();
-      cp_async_wait<1>();
-    }
-    __syncthreads();  // the tile (and, first time round, Qs / Ts) is in shared memory; the previous tile's scores are consumed
+  if (j_start <= j_end) load_rows(Ks, KP, k_off, kchunks, j_start);
+  for (int j0 = j_start; j0 <= j_end; j0 += KT) {
+    load_rows(Vs, VP, v_off, vchunks, j0);   // the value buffer is free: the previous tile ended with a barrier
+    cp_async_wait<1>();                      // this tile's keys have landed (its values may still be in flight)
+    __syncthreads();                         // ... for every thread; first time round Qs is complete as well
     float s[KT / 8][4];
 #pragma unroll
     for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
     if (warp_active) {
-      const uint32_t b_lane = ks_addr + (uint32_t)(((stage * KT + (lm >> 1) * 8 + lr) * KP + c_w * d + (lm & 1) * 8) * 2);
+      const uint32_t b_lane = ks_addr + (uint32_t)((((lm >> 1) * 8 + lr) * KP + c_w * d + (lm & 1) * 8) * 2);
       for (int kk = 0; kk < d; kk += 16) {
         uint32_t a[4];
         ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
@@ -312,7 +301,12 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
 #pragma unroll
         for (int nt = 0; nt < KT / 8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(s[nt][i * 2], s[nt][i * 2 + 1]);
       }
-      __syncthreads();
+    }
+    cp_async_wait<0>();   // this tile's values have landed
+    __syncthreads();      // scores and values are visible to all; nobody reads the key buffer any more
+    if (j0 + KT <= j_end) load_rows(Ks, KP, k_off, kchunks, j0 + KT);
+    else cp_async_commit();
+    if (talk) {
       if (warp_active) {
 #pragma unroll
         for (int nt = 0; nt < KT / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -320,16 +314,21 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (!valid[i]) continue;
-          const float* trow = Ts + h_row[i] * H;
+          const float* trow = talk + h_row[i] * H;
           const float* srow = Ss + tok_row[i] * rep * SP + cq;
-          for (int g = 0; g < H; ++g) {
-            const float tg = trow[g];
-            const float* ra = srow + ((g / rep) * rows_g + g % rep) * SP;
+          for (int c = 0; c < G; ++c) {   // head g = c * rep + hh of the same token: row c * rows_g + tok * rep + hh
+            const float* rc = srow + c * rows_g * SP;
+            const float* tc = trow + c * rep;
+#pragma unroll 4
+            for (int hh = 0; hh < rep; ++hh) {
+              const float tg = __ldg(tc + hh);
+              const float* ra = rc + hh * SP;
 #pragma unroll
-            for (int nt = 0; nt < KT / 8; ++nt) {
-              const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8);
-              s[nt][i * 2] = fmaf(tg, va.x, s[nt][i * 2]);
-              s[nt][i * 2 + 1] = fmaf(tg, va.y, s[nt][i * 2 + 1]);
+              for (int nt = 0; nt < KT / 8; ++nt) {
+                const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8);
+                s[nt][i * 2] = fmaf(tg, va.x, s[nt][i * 2]);
+                s[nt][i * 2 + 1] = fmaf(tg, va.y, s[nt][i * 2 + 1]);
+              }
             }
           }
         }
@@ -387,7 +386,7 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
         o[i][2] *= corr[1];
         o[i][3] *= corr[1];
       }
-      const uint32_t v_lane = vs_addr + (uint32_t)(((stage * KT + (lm & 1) * 8 + lr) * VP + c_w * dv + (lm >> 1) * 8) * 2);
+      const uint32_t v_lane = vs_addr + (uint32_t)((((lm & 1) * 8 + lr) * VP + c_w * dv + (lm >> 1) * 8) * 2);
 #pragma unroll
       for (int kg = 0; kg < KT / 16; ++kg) {
 #pragma unroll
@@ -399,7 +398,7 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
         }
       }
     }
-    __syncthreads();  // everyone is done with this stage (and with the scores) before the next iteration overwrites them
+    __syncthreads();  // everyone is done with the values and the scores before the next iteration overwrites them
   }
   if (gridDim.z > 1) {
     // partial [tile][split][R rows][dv + 2]: unnormalised output, then the running max and sum
@@ -527,11 +526,14 @@ static TalkPlan talk_mma_plan(int dt, int64_t T, int B, int H, int G, int d, int
   if (T > 2 * (int64_t)B)                                // prompts and portions: larger tiles share each key tile among more rows
     while ((int64_t)QT * 2 * H <= 128) QT *= 2;
   const int R = QT * H;
-  for (int KT : {64, 32, 16}) {
-    const size_t smem = ((size_t)R * (d + kTalkPad) + (size_t)2 * KT * (G * d + kTalkPad) + (size_t)2 * KT * (G * dv + kTalkPad)) * 2 +
-                        ((size_t)R * (KT + 8) + (has_talk ? (size_t)H * H : 0)) * 4;
-    if (smem <= 200 * 1024) { p.QT = QT; p.KT = KT; p.smem = smem; return p; }
-  }
+  (void)has_talk;
+  auto bytes = [&](int KT) {
+    return ((size_t)R * (d + kTalkPad) + (size_t)KT * (G * d + kTalkPad) + (size_t)KT * (G * dv + kTalkPad)) * 2 + (size_t)R * (KT + 4) * 4;
+  };
+  // the largest key tile with which two blocks share an SM; failing that, the largest that fits at all
+  for (size_t limit : {(size_t)112 * 1024, (size_t)200 * 1024})
+    for (int KT : {64, 32, 16})
+      if (bytes(KT) <= limit) { p.QT = QT; p.KT = KT; p.smem = bytes(KT); return p; }
   return p;
 }
 
