@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
   __nv_bfloat16* Ks = Qs + R * DP;                                   // [KT][KP]
   __nv_bfloat16* Vs = Ks + KT * KP;                                  // [KT][VP]
   float* Ss = reinterpret_cast<float*>(Vs + KT * VP);                // [R][SP] scaled raw scores of the tile
+  float* Ts = Ss + R * SP;                                           // [H][H] the mixing matrix
   int b, row0 = 0, ntok = 0;
   talk_find_tile(cu_q, B, QT, blockIdx.x, b, row0, ntok);
   if (b >= B) return;  // block-uniform: no barrier has been met yet
@@ -226,6 +227,8 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
     const bool live = tok < ntok;
     for (int i = lane; i < d; i += 32) Qs[r * DP + i] = __float2bfloat16_rn(live ? src[i] : 0.f);
   }
+  if (talk)
+    for (int i = threadIdx.x; i < H * H; i += nthreads) Ts[i] = talk[i];
   const int kchunks = KD / 8, vchunks = VD / 8;
   const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
   // one block-table lookup per thread and row, then the row's 16-byte pieces go round eight threads
@@ -314,14 +317,14 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (!valid[i]) continue;
-          const float* trow = talk + h_row[i] * H;
+          const float* trow = Ts + h_row[i] * H;
           const float* srow = Ss + tok_row[i] * rep * SP + cq;
           for (int c = 0; c < G; ++c) {   // head g = c * rep + hh of the same token: row c * rows_g + tok * rep + hh
             const float* rc = srow + c * rows_g * SP;
             const float* tc = trow + c * rep;
 #pragma unroll 4
             for (int hh = 0; hh < rep; ++hh) {
-              const float tg = __ldg(tc + hh);
+              const float tg = tc[hh];
               const float* ra = rc + hh * SP;
 #pragma unroll
               for (int nt = 0; nt < KT / 8; ++nt) {
@@ -526,12 +529,12 @@ static TalkPlan talk_mma_plan(int dt, int64_t T, int B, int H, int G, int d, int
   if (T > 2 * (int64_t)B)                                // prompts and portions: larger tiles share each key tile among more rows
     while ((int64_t)QT * 2 * H <= 128) QT *= 2;
   const int R = QT * H;
-  (void)has_talk;
   auto bytes = [&](int KT) {
-    return ((size_t)R * (d + kTalkPad) + (size_t)KT * (G * d + kTalkPad) + (size_t)KT * (G * dv + kTalkPad)) * 2 + (size_t)R * (KT + 4) * 4;
+    return ((size_t)R * (d + kTalkPad) + (size_t)KT * (G * d + kTalkPad) + (size_t)KT * (G * dv + kTalkPad)) * 2 +
+           ((size_t)R * (KT + 4) + (has_talk ? (size_t)H * H : 0)) * 4;
   };
-  // the largest key tile with which two blocks share an SM; failing that, the largest that fits at all
-  for (size_t limit : {(size_t)112 * 1024, (size_t)200 * 1024})
+  // the largest key tile with which two blocks share an SM (228 KB, 1 KB reserved per block); failing that, the largest that fits at all
+  for (size_t limit : {(size_t)(233472 / 2 - 1024), (size_t)200 * 1024})
     for (int KT : {64, 32, 16})
       if (bytes(KT) <= limit) { p.QT = QT; p.KT = KT; p.smem = bytes(KT); return p; }
   return p;
@@ -546,7 +549,7 @@ extern "C" int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G,
   const int64_t tiles = (T + p.QT - 1) / p.QT + B;
   const int64_t busy = (T + p.QT - 1) / p.QT > B ? (T + p.QT - 1) / p.QT : B;
   // as many runs as keep all blocks resident at once (shared memory decides how many share an SM)
-  int64_t per_sm = (int64_t)(220 * 1024) / (int64_t)(p.smem + 1024);
+  int64_t per_sm = (int64_t)233472 / (int64_t)(p.smem + 1024);   // 228 KB per SM, 1 KB reserved per block
   per_sm = per_sm < 1 ? 1 : per_sm;
   int64_t n = (148 * per_sm) / (busy > 0 ? busy : 1);
   n = n < 1 ? 1 : (n > 8 ? 8 : n);
