@@ -71,7 +71,7 @@ def noganex_config(name: str) -> dict:
     W = {"noganex-w2048": 2048, "noganex-w4096": 4096}[name]
     moe = {"kind": "moe", "expert": {"ff": W * 11 // 16}, "router": {"experts": 16, "top": 2, "scale": 2.5}, "shared": {"ff": W * 11 // 16}}
     attn = {"dim": 128, "heads": W // 128, "kv_heads": W // 512, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 2048},
-            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}}}
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "fast": 16.0, "original": 4096, "slow": 1.0}}}
     delta = {"conv": 4, "dim": 128, "heads": W // 128, "kv_heads": W // 256, "vdim": 128}
     layers = [
         {"type": "attention", "mixer": dict(attn), "mlp": {"kind": "dense", "ff": W * 11 // 4}},
