@@ -218,6 +218,11 @@ MIXER_CASES = [
                    "rot": {"base": 100.0, "dims": 16, "scaling": {"factor": 4.0, "fast": 8.0, "original": 32, "slow": 1.0}}}),
     ("attention", {"dim": 32, "heads": 4, "kv_heads": 4, "vdim": 16, "scale": 0.3, "mask": {"size": 33}, "rot": {"base": 100.0, "dims": 8}}),
     ("attention", {"dim": 64, "heads": 16, "kv_heads": 2, "vdim": 64, "scale": 0.2, "rot": {"base": 1000.0, "dims": 32}}),
+    # three heads per key head (a query tile of 16 tokens), the widest value size of the tensor-core kernel, and as many key heads as
+    # heads with too many rows for one block (plain kernel although the sizes are in 16s)
+    ("attention", {"dim": 32, "heads": 6, "kv_heads": 2, "vdim": 64, "scale": 0.3, "mask": {"size": 18}, "rot": {"base": 100.0, "dims": 32}}),
+    ("attention", {"dim": 32, "heads": 4, "kv_heads": 2, "vdim": 128, "scale": 0.3, "mask": {"size": 40}, "rot": {"base": 100.0, "dims": 16}}),
+    ("attention", {"dim": 16, "heads": 24, "kv_heads": 24, "vdim": 16, "scale": 0.4, "mask": {"size": 29}, "rot": {"base": 100.0, "dims": 16}}),
 ]
 
 
