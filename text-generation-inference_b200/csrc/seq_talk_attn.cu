@@ -179,6 +179,13 @@ __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
 // ------------------------------------------------------------------------------------------------------------------------
 constexpr int kTalkPad = 8;
 
+// acc += t * v on both halves at once (packed fp32 FMA of sm_100)
+__device__ __forceinline__ void ffma2(float2& acc, float t, float vx, float vy) {
+  asm("{ .reg .b64 a, b, c; mov.b64 a, {%2, %2}; mov.b64 b, {%3, %4}; mov.b64 c, {%0, %1}; fma.rn.f32x2 c, a, b, c; mov.b64 {%0, %1}, c; }"
+      : "+f"(acc.x), "+f"(acc.y)
+      : "f"(t), "f"(vx), "f"(vy));
+}
+
 // which (sequence, tile of QT of its rows) block `tile` has; b == B: none
 __device__ __forceinline__ void talk_find_tile(const int32_t* cu_q, int B, int QT, int tile, int& b, int& row0, int& ntok) {
   for (b = 0; b < B; ++b) {
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
     float* __restrict__ out, int H, int G, int d, int QT, int chunk, int window, float scale, int page, float* __restrict__ partial) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int dv = NDV * 8, SP = KT + 4;
+  constexpr int dv = NDV * 8, SP = KT == 16 ? 16 : KT + 4;   // row stride of the score tile: conflict-free 16-byte accesses
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int rep = H / G, R = QT * H, rows_g = QT * rep;
   const int KD = G * d, KP = KD + kTalkPad, VD = G * dv, VP = VD + kTalkPad, DP = d + kTalkPad;
@@ -297,12 +304,15 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
         for (int e = 0; e < 4; ++e) s[nt][e] *= scale;
     }
     if (talk) {
-      // all heads' scores of the tile meet in shared memory; every thread then mixes the elements of its own fragment
+      // all heads' scores of the tile meet in shared memory; every thread then mixes the elements of its own fragment.  A row of
+      // the tile is stored with each quad lane's KT / 4 columns side by side (the mix is column-wise, so any order serves as long
+      // as writer and reader agree), which makes the stores and the mix's loads 16 bytes wide
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        float* dst = Ss + (w * 16 + (lane >> 2) + i * 8) * SP + cq;
+        float* dst = Ss + (w * 16 + (lane >> 2) + i * 8) * SP + (lane & 3) * (KT / 4);
 #pragma unroll
-        for (int nt = 0; nt < KT / 8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(s[nt][i * 2], s[nt][i * 2 + 1]);
+        for (int nt = 0; nt < KT / 8; nt += 2)
+          *reinterpret_cast<float4*>(dst + nt * 2) = make_float4(s[nt][i * 2], s[nt][i * 2 + 1], s[nt + 1][i * 2], s[nt + 1][i * 2 + 1]);
       }
     }
     cp_async_wait<0>();   // this tile's values have landed
@@ -317,22 +327,46 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (!valid[i]) continue;
+          float2 acc[KT / 8];
+#pragma unroll
+          for (int nt = 0; nt < KT / 8; ++nt) acc[nt] = make_float2(0.f, 0.f);
           const float* trow = Ts + h_row[i] * H;
-          const float* srow = Ss + tok_row[i] * rep * SP + cq;
+          const float* srow = Ss + tok_row[i] * rep * SP + (lane & 3) * (KT / 4);
           for (int c = 0; c < G; ++c) {   // head g = c * rep + hh of the same token: row c * rows_g + tok * rep + hh
             const float* rc = srow + c * rows_g * SP;
             const float* tc = trow + c * rep;
-#pragma unroll 4
-            for (int hh = 0; hh < rep; ++hh) {
-              const float tg = tc[hh];
-              const float* ra = rc + hh * SP;
+            if ((rep & 3) == 0) {
+              for (int hh = 0; hh < rep; hh += 4) {
+                const float4 t4 = *reinterpret_cast<const float4*>(tc + hh);
+                const float tg[4] = {t4.x, t4.y, t4.z, t4.w};
 #pragma unroll
-              for (int nt = 0; nt < KT / 8; ++nt) {
-                const float2 va = *reinterpret_cast<const float2*>(ra + nt * 8);
-                s[nt][i * 2] = fmaf(tg, va.x, s[nt][i * 2]);
-                s[nt][i * 2 + 1] = fmaf(tg, va.y, s[nt][i * 2 + 1]);
+                for (int u = 0; u < 4; ++u) {
+                  const float* ra = rc + (hh + u) * SP;
+#pragma unroll
+                  for (int nt = 0; nt < KT / 8; nt += 2) {
+                    const float4 v = *reinterpret_cast<const float4*>(ra + nt * 2);
+                    ffma2(acc[nt], tg[u], v.x, v.y);
+                    ffma2(acc[nt + 1], tg[u], v.z, v.w);
+                  }
+                }
+              }
+            } else {
+              for (int hh = 0; hh < rep; ++hh) {
+                const float tg = tc[hh];
+                const float* ra = rc + hh * SP;
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; nt += 2) {
+                  const float4 v = *reinterpret_cast<const float4*>(ra + nt * 2);
+                  ffma2(acc[nt], tg, v.x, v.y);
+                  ffma2(acc[nt + 1], tg, v.z, v.w);
+                }
               }
             }
+          }
+#pragma unroll
+          for (int nt = 0; nt < KT / 8; ++nt) {
+            s[nt][i * 2] = acc[nt].x;
+            s[nt][i * 2 + 1] = acc[nt].y;
           }
         }
       }
@@ -531,7 +565,7 @@ static TalkPlan talk_mma_plan(int dt, int64_t T, int B, int H, int G, int d, int
   const int R = QT * H;
   auto bytes = [&](int KT) {
     return ((size_t)R * (d + kTalkPad) + (size_t)KT * (G * d + kTalkPad) + (size_t)KT * (G * dv + kTalkPad)) * 2 +
-           ((size_t)R * (KT + 4) + (has_talk ? (size_t)H * H : 0)) * 4;
+           ((size_t)R * (KT == 16 ? 16 : KT + 4) + (has_talk ? (size_t)H * H : 0)) * 4;
   };
   // the largest key tile with which two blocks share an SM (228 KB, 1 KB reserved per block); failing that, the largest that fits at all
   for (size_t limit : {(size_t)(233472 / 2 - 1024), (size_t)200 * 1024})
