@@ -130,19 +130,49 @@ int b200_seq_delta_scan(const float* c, int64_t ldc, int col_q, int col_k, int c
                         void* stream);
 /* per token: RMS norm over the whole q projection (H * d columns) and the whole k projection (G * d) when whole_norm != 0 (weights per
  * column, may be NULL), rotation of the first `rot` columns of every head, column i paired with i + rot / 2 (cos / sin fp32
- * [positions, rot / 2]); keys and values to the token-major cache row [k_off: G * d | v_off: G * dv], queries to q_out fp32 [T, H * d] */
+ * [positions, rot / 2]); keys and values to the token-major cache row [k_off: G * d | v_off: G * dv], queries to q_out fp32 [T, H * d].
+ * v_rot > 0: the first v_rot columns of every value head turn by the token's position too (vcos / vsin fp32 [positions, v_rot / 2];
+ * pairs are column i with i + v_rot / 2, or columns 2i and 2i + 1 when v_interleaved != 0) */
 int b200_seq_qk_rot_prepare(const float* src, int64_t ld, int col_q, int col_k, int col_v, int H, int G, int d, int dv, const void* qnorm_w,
                             const void* knorm_w, int whole_norm, float eps, const float* cos_t, const float* sin_t, int rot,
                             const int64_t* position_ids, const int64_t* slot_mapping, void* cache, int dt, int64_t row_width, int k_off,
-                            int v_off, float* q_out, int64_t T, void* stream);
+                            int v_off, float* q_out, int64_t T, const float* vcos_t, const float* vsin_t, int v_rot, int v_interleaved,
+                            void* stream);
 /* attention with the scaled scores mixed over the heads before the soft-max (talk fp32 [H, H], NULL: none); a query at p sees keys
- * j <= p with floor(j / chunk) == floor(p / chunk) (chunk > 0) and p - j < window (window > 0); out fp32 [T, H, dv] */
+ * j <= p with floor(j / chunk) == floor(p / chunk) (chunk > 0) and p - j < window (window > 0); sink fp32 [H] (NULL: none): exp(sink[h])
+ * joins head h's soft-max denominator (after the mix, unscaled) and carries no value; out fp32 [T, H, dv] */
 int b200_seq_talk_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids,
                        const float* talk, float* out, int64_t T, int H, int G, int d, int dv, int chunk, int window, float scale, int page,
-                       float* partial, int nsplit, void* stream);
+                       float* partial, int nsplit, const float* sink, void* stream);
 /* blocks to split each query tile's keys over for this step (0: plain kernel, 1: no split) and the fp32 workspace for `partial` */
 int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G, int d, int dv, int64_t* workspace_floats);
+/* several residual streams per token, X fp32 [T, S, W] in place (S <= 8).  init (fp32 [T, W], may be NULL): every stream starts as this
+ * row and X is not read.  y (fp32 [T, W], may be NULL): all streams at once from the old ones, X_t <- sum_s mix[s * S + t] X_s +
+ * out_coef[t] y.  in_coef (fp32 [S], may be NULL): u = sum_s in_coef[s] X_s of the new streams and typed (type dt) <-
+ * u / sqrt(mean u^2 + eps) * w (w of type dt; NULL: typed <- u) */
+int b200_seq_streams_step(float* X, int S, const float* init, const float* y, const float* mix, const float* out_coef, const float* in_coef,
+                          const void* w, int dt, void* typed, int64_t T, int64_t W, float eps, void* stream);
+/* out (dense rows of type out_dt) = act(in) over rows of F columns with leading dimension ld_in; act 0: SiLU, 1: GELU in its tanh form,
+ * 2: tanh; element types fp32 -> any or bf16 -> bf16 */
+int b200_seq_ff_act(const void* in, int in_dt, int64_t ld_in, void* out, int out_dt, int64_t rows, int64_t F, int act, void* stream);
+/* a fp32 [T, H, dv]: the first `rot` columns of every head turn by minus the token's position (cos / sin fp32 [positions, rot / 2]; pairs
+ * as in b200_seq_qk_rot_prepare's values), the head is multiplied by sigmoid(gate[t * ld_gate + h]) (gate NULL: by 1) and by out_scale
+ * -> out rows of type dt with leading dimension ld_out, H * dv columns written */
+int b200_seq_heads_turn_gate(const float* a, const float* gate, int64_t ld_gate, const float* cos_t, const float* sin_t, int rot,
+                             int interleaved, const int64_t* position_ids, void* out, int dt, int64_t ld_out, float out_scale, int64_t T, int H,
+                             int dv, void* stream);
+/* generalised delta rule over fp32 state slots S [slots, H, dk, dv]: per token, with u = k / sqrt(sum k^2 + 1e-6),
+ * S <- diag(w) S - (a * u)(u^T S) + k v^T (the old S on the right), y = S^T r; w = exp(-decay_scale sigmoid(dec[col_d + h dk + n] +
+ * w0[h dk + n])), a = sigmoid(raw[col_a + h dk + n] + a_bias[h dk + n]); r, k, a: H x dk columns of raw, v: H x dv; y fp32 [T, H * dv] */
+int b200_seq_gdelta_scan(const float* raw, int64_t ldr, int col_r, int col_k, int col_v, int col_a, const float* dec, int64_t ldd, int col_d,
+                         const void* a_bias, const void* w0, int dt, float decay_scale, float* S_state, const int32_t* state_slots,
+                         const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, void* stream);
+/* minimal gated recurrent unit over fp32 state slots [slots, C]: z = sigmoid(proj[col_z + c] + z_bias[c]), x = proj[col_x + c] + x_bias[c],
+ * candidate = x + 1/2 (x >= 0) or sigmoid(x), S <- (1 - z) S + z candidate; out (type out_dt) = S * SiLU(proj[col_g + c]) (col_g < 0: S), times out_scale */
+int b200_seq_mingru_scan(const float* proj, int64_t ld, int col_z, int col_x, int col_g, const void* z_bias, const void* x_bias, int dt,
+                         float* state, const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, void* out, int out_dt,
+                         int64_t ld_out, float out_scale, int B, int C, void* stream);
 
 #ifdef __cplusplus
 }

@@ -214,6 +214,120 @@ __global__ void ff_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, in
   }
 }
 
+// Several residual streams per token ("hyper-connections"): X [T, S, W] fp32.  One launch does what lies between two sublayers:
+//   write   (y given)        every stream at once from the old ones, X_t <- sum_s mix[s, t] X_s + out_coef[t] * y
+//   read    (in_coef given)  u = sum_s in_coef[s] X_s of the (new) streams; typed <- u / sqrt(mean(u^2) + eps) * w (w NULL: typed <- u)
+// `init`, when given, is the row every stream starts from (the embedding output) and X is not read.  One block per token; the
+// row of u waits in shared memory between the two passes; S <= kMaxStreams.
+constexpr int kMaxStreams = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) streams_step_kernel(float* __restrict__ X, int S, const float* __restrict__ init,
+                                                                   const float* __restrict__ y, const float* __restrict__ mix,
+                                                                   const float* __restrict__ out_coef, const float* __restrict__ in_coef,
+                                                                   const T* __restrict__ w, T* __restrict__ typed, int W, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  __shared__ float cm[kMaxStreams * kMaxStreams], co[kMaxStreams], ci[kMaxStreams];
+  if (threadIdx.x < S * S) cm[threadIdx.x] = mix ? mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    co[threadIdx.x] = out_coef ? out_coef[threadIdx.x] : 0.f;
+    ci[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  const int64_t t = blockIdx.x;
+  float* xr = X + t * S * W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    float x[kMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s)
+      if (s < S) x[s] = init ? init[t * W + i] : xr[(int64_t)s * W + i];
+    if (y) {
+      const float yv = y[t * W + i];
+      float nx[kMaxStreams];
+#pragma unroll
+      for (int u = 0; u < kMaxStreams; ++u) {
+        if (u >= S) break;
+        float a = co[u] * yv;
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s)
+          if (s < S) a = fmaf(cm[s * S + u], x[s], a);
+        nx[u] = a;
+      }
+#pragma unroll
+      for (int s = 0; s < kMaxStreams; ++s)
+        if (s < S) x[s] = nx[s];
+    }
+    if (y || init) {
+#pragma unroll
+      for (int s = 0; s < kMaxStreams; ++s)
+        if (s < S) xr[(int64_t)s * W + i] = x[s];
+    }
+    if (in_coef) {
+      float u = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxStreams; ++s)
+        if (s < S) u = fmaf(ci[s], x[s], u);
+      row[i] = u;
+      q += u * u;
+    }
+  }
+  if (!in_coef) return;
+  const float rstd = w ? 1.f / sqrtf(block_sum(q, red) / W + eps) : 1.f;
+  if (!w) __syncthreads();
+  for (int i = threadIdx.x; i < W; i += kRowThreads) stf(typed + t * W + i, w ? row[i] * rstd * ldf(w + i) : row[i]);
+}
+
+// out = act(in) element by element over rows of F columns (in may be a column slice: leading dimension ld_in);
+// act 0: SiLU, 1: GELU (tanh form), 2: tanh.  Evaluated in fp32.
+template <typename TI, typename TO, int ACT>
+__global__ void ff_act_kernel(const TI* __restrict__ in, int64_t ld_in, TO* __restrict__ out, int64_t rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * F;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / F, c = i % F;
+    const float z = ldf(in + r * ld_in + c);
+    stf(out + i, ACT == 1 ? gelu_tanh_f(z) : (ACT == 2 ? tanhf(z) : silu_f(z)));
+  }
+}
+
+// Attention heads on their way to the output projection: a [T, H, dv] fp32; every head's first `rot` columns are turned by
+// -position (pairs: column i with column i + rot / 2 when `interleaved` is 0, columns 2i and 2i + 1 otherwise; cos / sin
+// [positions, rot / 2]), then the head is multiplied by sigmoid(gate[t, h]) (gate NULL: by 1) and by out_scale -> out rows of
+// H * dv columns of type T (leading dimension ld_out: the rows may be a column slice of a wider buffer).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) heads_turn_gate_kernel(const float* __restrict__ a, const float* __restrict__ gate, int64_t ld_gate,
+                                                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                                                      int interleaved, const int64_t* __restrict__ position_ids,
+                                                                      T* __restrict__ out, int64_t ld_out, float out_scale, int H, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int half = rot / 2;
+  const float* cs = rot ? cos_t + position_ids[t] * half : nullptr;
+  const float* sn = rot ? sin_t + position_ids[t] * half : nullptr;
+  const float* row = a + t * H * dv;
+  for (int e = threadIdx.x; e < H * dv; e += kRowThreads) {
+    const int h = e / dv, i = e % dv;
+    float x = row[e];
+    if (i < rot) {
+      int f, partner;
+      bool first;
+      if (interleaved) { f = i >> 1; first = (i & 1) == 0; partner = first ? e + 1 : e - 1; }
+      else { first = i < half; f = first ? i : i - half; partner = first ? e + half : e - half; }
+      const float yv = row[partner];
+      // the inverse turn: (u, v) -> (u cos + v sin, v cos - u sin)
+      x = first ? x * cs[f] + yv * sn[f] : x * cs[f] - yv * sn[f];
+    }
+    if (gate) x *= sigmoid_f(gate[t * ld_gate + h]);
+    stf(out + t * ld_out + e, x * out_scale);
+  }
+}
+
 }  // namespace seq
 }  // namespace b200
 
@@ -357,6 +471,69 @@ extern "C" int b200_seq_ff_gate(const void* gu, void* out, int dt, int64_t rows,
   else
     B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((ff_gate_kernel<E, 0>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const E*)gu, (E*)out,
                                          rows, (int)F));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// X fp32 [T, S, W] in place (S <= 8).  init fp32 [T, W] or NULL; y fp32 [T, W] or NULL (with mix fp32 [S, S] indexed [from, to] and
+// out_coef fp32 [S]); in_coef fp32 [S] or NULL (with typed [T, W] of type dt and, optionally, the norm weight w of type dt).
+extern "C" int b200_seq_streams_step(float* X, int S, const float* init, const float* y, const float* mix, const float* out_coef,
+                                     const float* in_coef, const void* w, int dt, void* typed, int64_t T, int64_t W, float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  if (S < 1 || S > kMaxStreams || (y && (!mix || !out_coef)) || (in_coef && !typed) || W > 40000) {
+    b200_set_last_error("seq_streams_step: 1 <= streams <= 8; a write needs mix and out_coef, a read needs an output");
+    return B200_ERR_ARG;
+  }
+#define SST(E)                                                                                                                        \
+  do {                                                                                                                                \
+    static bool cfg = false;                                                                                                          \
+    if (!cfg) { cudaFuncSetAttribute(streams_step_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }  \
+    B200_LAUNCH((streams_step_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), (size_t)W * 4, (cudaStream_t)stream, X, S, init, y, mix, \
+                out_coef, in_coef, (const E*)w, (E*)typed, (int)W, eps);                                                              \
+  } while (0)
+  if (dt == B200_DT_F32) SST(float);
+  else if (dt == B200_DT_BF16) SST(__nv_bfloat16);
+  else { b200_set_last_error("unknown element type"); return B200_ERR_ARG; }
+#undef SST
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// in: rows of type in_dt (leading dimension ld_in), out: dense rows of type out_dt; act 0 SiLU, 1 GELU (tanh form), 2 tanh
+extern "C" int b200_seq_ff_act(const void* in, int in_dt, int64_t ld_in, void* out, int out_dt, int64_t rows, int64_t F, int act, void* stream) {
+  if (rows == 0 || F == 0) return B200_OK;
+  int64_t blocks = (rows * F + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act < 0 || act > 2) { b200_set_last_error("seq_ff_act: unknown activation"); return B200_ERR_ARG; }
+#define FA(TI, TO, A) B200_LAUNCH((ff_act_kernel<TI, TO, A>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const TI*)in, ld_in, (TO*)out, rows, (int)F)
+#define FA_ACT(TI, TO)            \
+  do {                            \
+    if (act == 0) FA(TI, TO, 0);  \
+    else if (act == 1) FA(TI, TO, 1); \
+    else FA(TI, TO, 2);           \
+  } while (0)
+  if (in_dt == B200_DT_F32 && out_dt == B200_DT_F32) FA_ACT(float, float);
+  else if (in_dt == B200_DT_F32 && out_dt == B200_DT_BF16) FA_ACT(float, __nv_bfloat16);
+  else if (in_dt == B200_DT_BF16 && out_dt == B200_DT_BF16) FA_ACT(__nv_bfloat16, __nv_bfloat16);
+  else { b200_set_last_error("seq_ff_act: element types must be fp32 -> any or bf16 -> bf16"); return B200_ERR_ARG; }
+#undef FA_ACT
+#undef FA
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// a fp32 [T, H, dv]; gate fp32 rows (leading dimension ld_gate, one logit per head) or NULL; cos / sin fp32 [positions, rot / 2]
+// (rot 0: no turn) -> out [T, ld_out] of type dt, H * dv columns written, times out_scale
+extern "C" int b200_seq_heads_turn_gate(const float* a, const float* gate, int64_t ld_gate, const float* cos_t, const float* sin_t, int rot,
+                                        int interleaved, const int64_t* position_ids, void* out, int dt, int64_t ld_out, float out_scale,
+                                        int64_t T, int H, int dv, void* stream) {
+  if (T == 0) return B200_OK;
+  if (rot < 0 || rot > dv || rot % 2 != 0 || (rot > 0 && (!cos_t || !sin_t || !position_ids))) {
+    b200_set_last_error("seq_heads_turn_gate: turned columns must be even, at most the head size, with tables and positions");
+    return B200_ERR_ARG;
+  }
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((heads_turn_gate_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, a, gate, ld_gate,
+                                       cos_t, sin_t, rot, interleaved, position_ids, (E*)out, ld_out, out_scale, H, dv));
   b200_count_launches(1);
   return B200_OK;
 }

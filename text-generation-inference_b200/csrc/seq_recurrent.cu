@@ -337,6 +337,142 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(
   }
 }
 
+// Generalised delta rule.  Per head a [dk, dv] memory; every token, with the unit key u = k / sqrt(sum k^2 + 1e-6):
+//   S <- diag(w) S - (a * u) (u^T S) + k v^T   (both subtrahend and decay read the old memory),   y = S^T r
+// w = exp(-decay_scale * sigmoid(dlogit + w0)) and a = sigmoid(alogit + a_bias) per head and key channel.
+// raw: rows holding r, k (H x dk each), v (H x dv) and the removal logits (H x dk); dec: rows holding the decay logits (H x dk).
+template <typename TP, int KMAX>
+__global__ void __launch_bounds__(kScanThreads) gdelta_scan_kernel(
+    const float* __restrict__ raw, int64_t ldr, int col_r, int col_k, int col_v, int col_a, const float* __restrict__ dec, int64_t ldd, int col_d,
+    const TP* __restrict__ a_bias, const TP* __restrict__ w0, float decay_scale, float* __restrict__ S_state, const int32_t* __restrict__ state_slots,
+    const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ y, int64_t ld_y, int H, int dk, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* rs = sm;                       // [kChunk][dk] read vector
+  float* kk = rs + kChunk * dk;         // [kChunk][dk] key
+  float* uu = kk + kChunk * dk;         // [kChunk][dk] unit key
+  float* au = uu + kChunk * dk;         // [kChunk][dk] removal rate times unit key
+  float* ws = au + kChunk * dk;         // [kChunk][dk] decay
+  float* vs = ws + kChunk * dk;         // [kChunk][kCols]
+  float* ys = vs + kChunk * kCols;      // [kChunk][kCols]
+  float* stage = ys + kChunk * kCols;   // [dk][kCols + 1]
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
+  const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (t_begin >= t_end) return;
+  const bool fresh = position_ids[t_begin] == 0;
+  float* Sp = S_state + ((int64_t)state_slots[b] * H + h) * dk * dv;
+  float S[KMAX];
+  if (!fresh) {
+    for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+      const int n = idx / kCols, cc = idx % kCols;
+      stage[n * (kCols + 1) + cc] = (v0 + cc < dv) ? Sp[(int64_t)n * dv + v0 + cc] : 0.f;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    S[i] = (!fresh && n < dk) ? stage[n * (kCols + 1) + col] : 0.f;
+  }
+  for (int t0 = t_begin; t0 < t_end; t0 += kChunk) {
+    const int nt = min(kChunk, t_end - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * dk; idx += kScanThreads) {
+      const int tt = idx / dk, n = idx % dk;
+      const float* row = raw + (int64_t)(t0 + tt) * ldr;
+      rs[idx] = row[col_r + h * dk + n];
+      kk[idx] = row[col_k + h * dk + n];
+      au[idx] = sigmoid_f(row[col_a + h * dk + n] + ldf(a_bias + h * dk + n));
+      ws[idx] = expf(-decay_scale * sigmoid_f(dec[(int64_t)(t0 + tt) * ldd + col_d + h * dk + n] + ldf(w0 + h * dk + n)));
+    }
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, cc = idx % kCols;
+      vs[idx] = (v0 + cc < dv) ? raw[(int64_t)(t0 + tt) * ldr + col_v + h * dv + v0 + cc] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = warp_id(); tt < nt; tt += kScanThreads / 32) {  // unit key, one warp per token
+      float sk = 0.f;
+      for (int n = lane_id(); n < dk; n += 32) sk = fmaf(kk[tt * dk + n], kk[tt * dk + n], sk);
+      const float rk = 1.f / sqrtf(warp_sum(sk) + 1e-6f);
+      for (int n = lane_id(); n < dk; n += 32) {
+        const float u = kk[tt * dk + n] * rk;
+        uu[tt * dk + n] = u;
+        au[tt * dk + n] *= u;
+      }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      float along = 0.f;   // u^T S of this column, from the old memory
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) along = fmaf(S[i], uu[tt * dk + n], along);
+      }
+      along = group8_sum(along);
+      const float vv = vs[tt * kCols + col];
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) {
+          S[i] = fmaf(kk[tt * dk + n], vv, fmaf(-au[tt * dk + n], along, ws[tt * dk + n] * S[i]));
+          o = fmaf(S[i], rs[tt * dk + n], o);
+        }
+      }
+      o = group8_sum(o);
+      if (ks == 0) ys[tt * kCols + col] = o;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, cc = idx % kCols;
+      if (v0 + cc < dv) y[(int64_t)(t0 + tt) * ld_y + h * dv + v0 + cc] = ys[idx];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    if (n < dk) stage[n * (kCols + 1) + col] = S[i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+    const int n = idx / kCols, cc = idx % kCols;
+    if (v0 + cc < dv) Sp[(int64_t)n * dv + v0 + cc] = stage[n * (kCols + 1) + cc];
+  }
+}
+
+// Minimal gated recurrent unit: per channel S <- (1 - z) S + z c with z = sigmoid(zlogit + z_bias) and the candidate
+// c = x + 1/2 for x >= 0, sigmoid(x) below (x = xlogit + x_bias); out = S * SiLU(gate) * out_scale in the projections' element type.
+// One thread per (sequence, channel) walks the sequence's rows of the step in order.
+constexpr int kGruThreads = 128;
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kGruThreads) mingru_scan_kernel(const float* __restrict__ proj, int64_t ld, int col_z, int col_x, int col_g,
+                                                                  const TP* __restrict__ z_bias, const TP* __restrict__ x_bias,
+                                                                  float* __restrict__ state, const int32_t* __restrict__ state_slots,
+                                                                  const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids,
+                                                                  TO* __restrict__ out, int64_t ld_out, float out_scale, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, c = blockIdx.y * kGruThreads + threadIdx.x;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (c >= C || t_begin >= t_end) return;
+  float* sp = state + (int64_t)state_slots[b] * C + c;
+  float S = position_ids[t_begin] == 0 ? 0.f : *sp;
+  const float zb = z_bias ? ldf(z_bias + c) : 0.f, xb = x_bias ? ldf(x_bias + c) : 0.f;
+#pragma unroll 4
+  for (int t = t_begin; t < t_end; ++t) {
+    const float* row = proj + (int64_t)t * ld;
+    const float z = sigmoid_f(row[col_z + c] + zb), x = row[col_x + c] + xb;
+    const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
+    S = fmaf(z, cand - S, S);
+    stf(out + (int64_t)t * ld_out + c, (col_g >= 0 ? S * silu_f(row[col_g + c]) : S) * out_scale);
+  }
+  *sp = S;
+}
+
 constexpr int kMaxTaps = 8;
 
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in(p - (taps-1) + j)), p the token's position; inputs before this step's first token
@@ -522,4 +658,57 @@ extern "C" int b200_seq_delta_scan(const float* c, int64_t ldc, int col_q, int c
   else if (dk <= 128) DL(16);
   else DL(32);
 #undef DL
+}
+
+template <typename TP, int KMAX>
+static int launch_gdelta(const float* raw, int64_t ldr, int col_r, int col_k, int col_v, int col_a, const float* dec, int64_t ldd, int col_d,
+                         const void* a_bias, const void* w0, float decay_scale, float* S_state, const int32_t* state_slots, const int32_t* cu_q,
+                         const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, cudaStream_t st) {
+  const size_t smem = ((size_t)5 * kChunk * dk + 2 * kChunk * kCols + (size_t)dk * (kCols + 1)) * 4;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(gdelta_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
+  dim3 grid((unsigned)B, (unsigned)H, (unsigned)((dv + kCols - 1) / kCols));
+  B200_LAUNCH((gdelta_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, raw, ldr, col_r, col_k, col_v, col_a, dec, ldd, col_d,
+              (const TP*)a_bias, (const TP*)w0, decay_scale, S_state, state_slots, cu_q, position_ids, y, ld_y, H, dk, dv);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// raw fp32 [T, ldr]: read vectors, keys (H x dk each), values (H x dv) and removal logits (H x dk) at col_r / col_k / col_v / col_a;
+// dec fp32 [T, ldd]: decay logits (H x dk) at col_d; a_bias, w0 [H * dk] of element type dt; S_state fp32 [slots, H, dk, dv] advanced
+// in place -> y fp32 [T, H * dv]
+extern "C" int b200_seq_gdelta_scan(const float* raw, int64_t ldr, int col_r, int col_k, int col_v, int col_a, const float* dec, int64_t ldd,
+                                    int col_d, const void* a_bias, const void* w0, int dt, float decay_scale, float* S_state,
+                                    const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B,
+                                    int H, int dk, int dv, void* stream) {
+  if (B == 0) return B200_OK;
+  if (dk <= 0 || dk > 256 || dv <= 0) { b200_set_last_error("seq_gdelta_scan: need 0 < key size <= 256"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+#define GD(K)                                                                                                                                \
+  B200_SEQ_DISPATCH(dt, E, return (launch_gdelta<E, K>(raw, ldr, col_r, col_k, col_v, col_a, dec, ldd, col_d, a_bias, w0, decay_scale, S_state, \
+                                                      state_slots, cu_q, position_ids, y, ld_y, B, H, dk, dv, st)))
+  if (dk <= 64) GD(8);
+  else if (dk <= 128) GD(16);
+  else GD(32);
+#undef GD
+}
+
+// proj fp32 [T, ld]: update-gate logits, candidate inputs and output-gate logits (C columns each) at col_z / col_x / col_g (col_g < 0:
+// no output gate); z_bias, x_bias [C] of element type dt (may be NULL); state fp32 [slots, C] advanced in place -> out [T, ld_out] of
+// type out_dt, times out_scale
+extern "C" int b200_seq_mingru_scan(const float* proj, int64_t ld, int col_z, int col_x, int col_g, const void* z_bias, const void* x_bias, int dt,
+                                    float* state, const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, void* out,
+                                    int out_dt, int64_t ld_out, float out_scale, int B, int C, void* stream) {
+  if (B == 0 || C == 0) return B200_OK;
+  dim3 grid((unsigned)B, (unsigned)((C + kGruThreads - 1) / kGruThreads));
+  cudaStream_t st = (cudaStream_t)stream;
+#define MG(TO)                                                                                                                          \
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((mingru_scan_kernel<E, TO>), grid, dim3(kGruThreads), 0, st, proj, ld, col_z, col_x, col_g,      \
+                                       (const E*)z_bias, (const E*)x_bias, state, state_slots, cu_q, position_ids, (TO*)out, ld_out, out_scale, C))
+  if (out_dt == B200_DT_F32) MG(float);
+  else if (out_dt == B200_DT_BF16) MG(__nv_bfloat16);
+  else { b200_set_last_error("unknown element type"); return B200_ERR_ARG; }
+#undef MG
+  b200_count_launches(1);
+  return B200_OK;
 }

@@ -11,7 +11,8 @@
 //                           whole k projection (one statistic for all heads, a weight per column), rotation of the first
 //                           `rot` columns of every head in the rotate-half layout (column i pairs with column i + rot/2; the
 //                           cos / sin tables carry frequency scaling and amplitude), keys and values into the token's cache
-//                           slot, queries into a dense fp32 buffer.
+//                           slot, queries into a dense fp32 buffer.  Optionally the values turn as well, by their own position
+//                           over the first `v_rot` columns of every value head (halves or neighbouring columns as pairs).
 //   talk_attn_kernel      : plain form, any element type and shape.  One block per (query token, slab of 8 heads): raw scores of
 //                           all heads against a tile of 32 keys, the mix, fp32 online soft-max and P V for the slab's heads (a
 //                           warp each).  Prompts, portions and decoded tokens are one case: keys come back from the cache.
@@ -30,7 +31,7 @@ __global__ void __launch_bounds__(kTalkPrepThreads) qk_rot_prepare_kernel(
     const float* __restrict__ src, int64_t ld, int col_q, int col_k, int col_v, int H, int G, int d, int dv, const T* __restrict__ qnorm_w,
     const T* __restrict__ knorm_w, int whole_norm, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
     const int64_t* __restrict__ position_ids, const int64_t* __restrict__ slot_mapping, T* __restrict__ cache, int64_t RW, int k_off, int v_off,
-    float* __restrict__ q_out) {
+    float* __restrict__ q_out, const float* __restrict__ vcos_t, const float* __restrict__ vsin_t, int v_rot, int v_interleaved) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[32];
@@ -67,8 +68,25 @@ __global__ void __launch_bounds__(kTalkPrepThreads) qk_rot_prepare_kernel(
     if (is_q) q_out[t * nq + c] = x;
     else if (crow) stf(crow + k_off + c, x);
   }
-  if (crow)
-    for (int c = threadIdx.x; c < G * dv; c += kTalkPrepThreads) stf(crow + v_off + c, row[col_v + c]);
+  if (crow) {
+    // values: the first v_rot columns of every value head turn with the token's own position (tables of their own)
+    const int vhalf = v_rot / 2;
+    const float* vc = v_rot ? vcos_t + pos * vhalf : nullptr;
+    const float* vs = v_rot ? vsin_t + pos * vhalf : nullptr;
+    for (int c = threadIdx.x; c < G * dv; c += kTalkPrepThreads) {
+      const int i = c % dv;
+      float x = row[col_v + c];
+      if (i < v_rot) {
+        int f, partner;
+        bool first;
+        if (v_interleaved) { f = i >> 1; first = (i & 1) == 0; partner = first ? c + 1 : c - 1; }
+        else { first = i < vhalf; f = first ? i : i - vhalf; partner = first ? c + vhalf : c - vhalf; }
+        const float y = row[col_v + partner];
+        x = first ? x * vc[f] - y * vs[f] : x * vc[f] + y * vs[f];
+      }
+      stf(crow + v_off + c, x);
+    }
+  }
 }
 
 constexpr int kTalkWarps = 8, kTalkKeys = 32;
@@ -83,7 +101,7 @@ template <typename T, int NV>  // NV = ceil(vdim / 32) value columns per lane
 __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
     const float* __restrict__ q, const T* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
     int64_t bt_stride, const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, const float* __restrict__ talk,
-    float* __restrict__ out, int H, int G, int d, int dv, int chunk, int window, float scale, int page) {
+    float* __restrict__ out, int H, int G, int d, int dv, int chunk, int window, float scale, int page, const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -99,7 +117,8 @@ __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
   const int p = (int)position_ids[t];
   const int j_lo = first_visible(p, chunk, window);
   for (int idx = threadIdx.x; idx < H * d; idx += nthreads) qs[idx] = q[t * H * d + idx] * scale;
-  float m = -INFINITY, l = 0.f, acc[NV];
+  // a sink logit sits in the soft-max denominator like one more key (unscaled, never mixed) whose value is zero
+  float m = (sink && own) ? sink[h] : -INFINITY, l = (sink && own) ? 1.f : 0.f, acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) acc[i] = 0.f;
   const int32_t* table = block_table + (int64_t)b * bt_stride;
@@ -204,7 +223,8 @@ template <int NDV, int KT>  // NDV = vdim / 8 output n-tiles per warp, KT keys p
 __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
     const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
     int64_t bt_stride, const int32_t* __restrict__ cu_q, int B, const int64_t* __restrict__ position_ids, const float* __restrict__ talk,
-    float* __restrict__ out, int H, int G, int d, int QT, int chunk, int window, float scale, int page, float* __restrict__ partial) {
+    float* __restrict__ out, int H, int G, int d, int QT, int chunk, int window, float scale, int page, float* __restrict__ partial,
+    const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int dv = NDV * 8, SP = KT == 16 ? 16 : KT + 4;   // row stride of the score tile: conflict-free 16-byte accesses
@@ -271,6 +291,13 @@ __global__ void __launch_bounds__(512) talk_attn_mma_kernel(
   const bool warp_active = ((w * 16) % rows_g) / rep < ntok;  // rows of a warp ascend in token: its first row decides
   const int lo_last = first_visible(p_last, chunk, window);
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  if (sink && blockIdx.z == 0) {   // the sink counts once: in the first run of the keys
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      m_run[i] = sink[h_row[i]];
+      l_run[i] = 1.f;
+    }
+  }
   float o[NDV][4];
 #pragma unroll
   for (int i = 0; i < NDV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -515,18 +542,24 @@ using namespace b200::seq;
 
 // src fp32 [T, ld] holds the projections at columns col_q (H * d), col_k (G * d), col_v (G * dv).  whole_norm: RMS norm over each of
 // the q and k projections as a whole (weights per column, may be NULL).  cos / sin fp32 [positions, rot / 2]; rot 0: no rotation.
+// vcos / vsin fp32 [positions, v_rot / 2]: the values' own turn (v_rot 0: stored as projected; v_interleaved: pairs are neighbours).
 extern "C" int b200_seq_qk_rot_prepare(const float* src, int64_t ld, int col_q, int col_k, int col_v, int H, int G, int d, int dv,
                                        const void* qnorm_w, const void* knorm_w, int whole_norm, float eps, const float* cos_t, const float* sin_t,
                                        int rot, const int64_t* position_ids, const int64_t* slot_mapping, void* cache, int dt, int64_t row_width,
-                                       int k_off, int v_off, float* q_out, int64_t T, void* stream) {
+                                       int k_off, int v_off, float* q_out, int64_t T, const float* vcos_t, const float* vsin_t, int v_rot,
+                                       int v_interleaved, void* stream) {
   if (T == 0) return B200_OK;
+  if (v_rot < 0 || v_rot > dv || v_rot % 2 != 0 || (v_rot > 0 && (vcos_t == nullptr || vsin_t == nullptr))) {
+    b200_set_last_error("seq_qk_rot_prepare: turned value columns must be even, at most the value size, with tables");
+    return B200_ERR_ARG;
+  }
   if (rot < 0 || rot > d || rot % 2 != 0 || (rot > 0 && (cos_t == nullptr || sin_t == nullptr))) {
     b200_set_last_error("seq_qk_rot_prepare: rotated columns must be even, at most the head size, with tables");
     return B200_ERR_ARG;
   }
   B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((qk_rot_prepare_kernel<E>), dim3((unsigned)T), dim3(kTalkPrepThreads), 0, (cudaStream_t)stream, src, ld, col_q,
                                        col_k, col_v, H, G, d, dv, (const E*)qnorm_w, (const E*)knorm_w, whole_norm, eps, cos_t, sin_t, rot,
-                                       position_ids, slot_mapping, (E*)cache, row_width, k_off, v_off, q_out));
+                                       position_ids, slot_mapping, (E*)cache, row_width, k_off, v_off, q_out, vcos_t, vsin_t, v_rot, v_interleaved));
   b200_count_launches(1);
   return B200_OK;
 }
@@ -534,7 +567,7 @@ extern "C" int b200_seq_qk_rot_prepare(const float* src, int64_t ld, int col_q, 
 template <typename E, int NV>
 static int launch_talk_plain(const float* q, const void* cache, int64_t RW, int k_off, int v_off, const int32_t* block_table, int64_t bt_stride,
                              const int32_t* seq_of_token, const int64_t* position_ids, const float* talk, float* out, int64_t T, int H, int G, int d,
-                             int dv, int chunk, int window, float scale, int page, cudaStream_t st) {
+                             int dv, int chunk, int window, float scale, int page, const float* sink, cudaStream_t st) {
   const size_t kvbuf = (size_t)kTalkKeys * (size_t)max(G * d + 1, G * dv);
   const size_t smem = ((size_t)H * d + (size_t)H * kTalkKeys + kvbuf) * 4;
   if (smem > 200 * 1024) { b200_set_last_error("seq_talk_attn: heads x size too large for the plain kernel"); return B200_ERR_UNSUPPORTED; }
@@ -542,7 +575,7 @@ static int launch_talk_plain(const float* q, const void* cache, int64_t RW, int 
   if (!cfg) { cudaFuncSetAttribute(talk_attn_kernel<E, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; }
   dim3 grid((unsigned)T, (unsigned)((H + kTalkWarps - 1) / kTalkWarps));
   B200_LAUNCH((talk_attn_kernel<E, NV>), grid, dim3(kTalkWarps * 32), smem, st, q, (const E*)cache, RW, k_off, v_off, block_table, bt_stride,
-              seq_of_token, position_ids, talk, out, H, G, d, dv, chunk, window, scale, page);
+              seq_of_token, position_ids, talk, out, H, G, d, dv, chunk, window, scale, page, sink);
   b200_count_launches(1);
   return B200_OK;
 }
@@ -592,11 +625,12 @@ extern "C" int b200_seq_talk_attn_splits(int dt, int64_t T, int B, int H, int G,
 }
 
 // q fp32 [T, H, d]; cache rows as above; talk fp32 [H, H] or NULL (no mix); chunk / window <= 0: none -> out fp32 [T, H, dv].
+// sink fp32 [H] or NULL: a logit per head that joins the soft-max denominator (after the mix, unscaled) and carries no value.
 // `partial` / nsplit: from b200_seq_talk_attn_splits (NULL / <= 1: no split).
 extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
                                   int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids,
                                   const float* talk, float* out, int64_t T, int H, int G, int d, int dv, int chunk, int window, float scale,
-                                  int page, float* partial, int nsplit, void* stream) {
+                                  int page, float* partial, int nsplit, const float* sink, void* stream) {
   if (T == 0) return B200_OK;
   if (G <= 0 || H % G != 0 || d <= 0 || dv <= 0 || dv > 256) {
     b200_set_last_error("seq_talk_attn: need heads % kv_heads == 0 and 0 < vdim <= 256");
@@ -616,7 +650,7 @@ extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int
     static bool cfg = false;                                                                                                             \
     if (!cfg) { cudaFuncSetAttribute(talk_attn_mma_kernel<N, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
     B200_LAUNCH((talk_attn_mma_kernel<N, KT>), grid, dim3(threads), plan.smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
-                block_table, bt_stride, cu_q, B, position_ids, talk, out, H, G, d, plan.QT, chunk, window, scale, page, partial);        \
+                block_table, bt_stride, cu_q, B, position_ids, talk, out, H, G, d, plan.QT, chunk, window, scale, page, partial, sink);  \
   } while (0)
 #define TAM_KT(N)                 \
   do {                            \
@@ -640,7 +674,7 @@ extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int
   }
 #define TALK(N)                                                                                                                              \
   B200_SEQ_DISPATCH(dt, E, return (launch_talk_plain<E, N>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, position_ids, \
-                                                          talk, out, T, H, G, d, dv, chunk, window, scale, page, st)))
+                                                          talk, out, T, H, G, d, dv, chunk, window, scale, page, sink, st)))
   const int nv = (dv + 31) / 32;
   if (nv <= 1) TALK(1);
   else if (nv <= 2) TALK(2);

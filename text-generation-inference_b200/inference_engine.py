@@ -18,9 +18,9 @@ import torch.distributed
 from .utils.dist import initialize_torch_distributed
 from .utils.weights import Weights
 
-FLASH_TYPES = ["llama", "gpt_neox", "gpt_bigcode", "falcon", "RefinedWeb", "RefinedWebModel", "fetotar", "dubesun", "noganex"]
+FLASH_TYPES = ["llama", "gpt_neox", "gpt_bigcode", "falcon", "RefinedWeb", "RefinedWebModel", "fetotar", "dubesun", "noganex", "nasozen"]
 # families whose config.json is not a transformers configuration: they name themselves with "architecture"
-OWN_CONFIG_ARCHITECTURES = ("Fetotar", "Dubesun", "Noganex")
+OWN_CONFIG_ARCHITECTURES = ("Fetotar", "Dubesun", "Noganex", "Nasozen")
 _TOKENIZER_FILES = ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json")
 
 
@@ -39,6 +39,9 @@ def load_config(model_path: str):
     if raw.get("architecture") == "Noganex":
         from .models.custom_modeling.noganex_modeling import NoganexConfig
         return NoganexConfig(raw)
+    if raw.get("architecture") == "Nasozen":
+        from .models.custom_modeling.nasozen_modeling import NasozenConfig
+        return NasozenConfig(raw)
     from transformers import AutoConfig
     return AutoConfig.from_pretrained(model_path)
 
@@ -96,7 +99,7 @@ class InferenceEngine:
                 raise NotImplementedError("alibi is not supported by this version of the model")
             from .models.custom_modeling.flash_rw_modeling import FlashRWForCausalLM
             model_class = FlashRWForCausalLM
-        elif model_type in ("fetotar", "dubesun", "noganex"):
+        elif model_type in ("fetotar", "dubesun", "noganex", "nasozen"):
             if quantize is not None:
                 raise ValueError(f"{model_type} checkpoints are served in bfloat16 or float32")
             if dtype not in (torch.bfloat16, torch.float32):
@@ -105,8 +108,10 @@ class InferenceEngine:
                 from .models.custom_modeling.fetotar_modeling import FetotarForCausalLM as model_class
             elif model_type == "dubesun":
                 from .models.custom_modeling.dubesun_modeling import DubesunForCausalLM as model_class
-            else:
+            elif model_type == "noganex":
                 from .models.custom_modeling.noganex_modeling import NoganexForCausalLM as model_class
+            else:
+                from .models.custom_modeling.nasozen_modeling import NasozenForCausalLM as model_class
         self._config.quantize = quantize
         self.process_group = initialize_torch_distributed(self.world_size, self.rank)
         self.master = self.rank == 0

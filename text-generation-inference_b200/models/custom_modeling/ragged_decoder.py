@@ -3,7 +3,8 @@ the cache manager they ask for (block pool + state slots, utils/paged.py `Hybrid
 signature over a `RaggedStep`, and the fused greedy step protocol of `FlashCausalLM._decode_fused_greedy`.
 
 A family subclasses `RaggedDecoderForCausalLM` and gives it `self.model`: a module with `layers` (each with a `.mixer` that has
-`cache_spec()`), `final_norm`, `kv_cache_manager`, and `forward(input_ids, step, max_s) -> fp32 stream [T, width]`.
+`cache_spec()`), `final_norm`, `kv_cache_manager`, and `forward(input_ids, step, max_s) -> fp32 stream [T, width]` (or whatever its `final_norm` takes
+per token row: a family with several streams returns [T, streams, width]).
 """
 from __future__ import annotations
 
@@ -38,14 +39,15 @@ class RaggedDecoderForCausalLM(nn.Module):
         bookkeeping), as for the other Python-driven families; B200_PY_FUSED_STEP=0 keeps it op by op"""
         return os.environ.get("B200_PY_FUSED_STEP", "") != "0"
 
-    def __init__(self, config, weights, model: nn.Module):
+    def __init__(self, config, weights, model: nn.Module, head_tensor: str = "head"):
+        """`head_tensor`: the checkpoint tensor of the vocabulary head ("embed" for a family whose embedding table is its head)"""
         super().__init__()
         self.config = config
         self.process_group = weights.process_group
         self.device = torch.device(weights.device)
         self.dtype = weights.dtype
         self.model = model
-        self.head = weights.get_tensor("head").contiguous()
+        self.head = model.embed if head_tensor == "embed" and hasattr(model, "embed") else weights.get_tensor(head_tensor).contiguous()
         self.lm_head = _HeadView(self.head)
 
     @property
@@ -62,7 +64,9 @@ class RaggedDecoderForCausalLM(nn.Module):
     def prepare_positions(self, max_s: int) -> None:
         """grows whatever per-position tables the layers keep, so that nothing is allocated inside a captured graph"""
         for layer in self.model.layers:
-            if getattr(layer.mixer, "rotary", None) is not None:
+            if hasattr(layer.mixer, "prepare_positions"):      # a mixer with several tables, or with mixers of its own
+                layer.mixer.prepare_positions(int(max_s) + 1, self.device)
+            elif getattr(layer.mixer, "rotary", None) is not None:
                 layer.mixer.rotary.tables(int(max_s) + 1, self.device)
 
     def make_cache_manager(self, dtype, device, num_blocks: Optional[int], num_state_slots: Optional[int]) -> HybridCacheManager:

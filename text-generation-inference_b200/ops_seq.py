@@ -469,31 +469,38 @@ def delta_scan(c: torch.Tensor, col_q: int, col_k: int, col_v: int, raw: torch.T
 
 def qk_rot_prepare(src: torch.Tensor, *, col_q: int, col_k: int, col_v: int, heads: int, kv_heads: int, dim: int, vdim: int,
                    q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], whole_norm: bool, eps: float, cos: Optional[torch.Tensor],
-                   sin: Optional[torch.Tensor], rot: int, step: RaggedStep, cache: torch.Tensor, k_off: int, v_off: int) -> torch.Tensor:
+                   sin: Optional[torch.Tensor], rot: int, step: RaggedStep, cache: torch.Tensor, k_off: int, v_off: int,
+                   v_cos: Optional[torch.Tensor] = None, v_sin: Optional[torch.Tensor] = None, v_rot: int = 0, v_interleaved: bool = False
+                   ) -> torch.Tensor:
     """src fp32 [T, C] = [q | k | v] projections: RMS norm over the whole q and the whole k projection (whole_norm), rotation of the
     first `rot` columns of every head in the rotate-half layout with the cos / sin tables, keys and values into the token's row of
-    `cache` [blocks, page, row] (token-major: keys of all key heads from k_off, values from v_off) -> queries fp32 [T, heads, dim]."""
-    _cuda(src, cache, q_norm_w, k_norm_w, cos, sin)
+    `cache` [blocks, page, row] (token-major: keys of all key heads from k_off, values from v_off) -> queries fp32 [T, heads, dim].
+    v_rot > 0: the first v_rot columns of every value head turn by the token's position as well, with tables of their own
+    (v_cos / v_sin [positions, v_rot / 2]); pairs are column i with i + v_rot / 2, or neighbours (v_interleaved)."""
+    _cuda(src, cache, q_norm_w, k_norm_w, cos, sin, v_cos, v_sin)
     assert src.dtype == torch.float32 and src.stride(1) == 1 and cache.is_contiguous()
     assert rot == 0 or (cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == rot // 2)
+    assert v_rot == 0 or (v_cos.dtype == torch.float32 and v_cos.is_contiguous() and v_sin.is_contiguous() and v_cos.shape[1] == v_rot // 2)
     q = torch.empty(step.T, heads, dim, dtype=torch.float32, device=src.device)
     _lib.check_seq(_lib.load_seq().b200_seq_qk_rot_prepare(
         _ptr(src), src.stride(0), col_q, col_k, col_v, heads, kv_heads, dim, vdim, _ptr(q_norm_w), _ptr(k_norm_w), int(whole_norm), float(eps),
         _ptr(cos), _ptr(sin), int(rot), _ptr(step.position_ids), _ptr(step.slot_mapping), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off,
-        _ptr(q), step.T, _stream()), "seq_qk_rot_prepare")
+        _ptr(q), step.T, _ptr(v_cos), _ptr(v_sin), int(v_rot), int(v_interleaved), _stream()), "seq_qk_rot_prepare")
     return q
 
 
 def talk_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, kv_heads: int, vdim: int, k_off: int, v_off: int, scale: float,
-              talk: Optional[torch.Tensor] = None, chunk: int = 0, window: int = 0) -> torch.Tensor:
+              talk: Optional[torch.Tensor] = None, chunk: int = 0, window: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q fp32 [T, heads, dim]; cache [blocks, page, row] token-major as `qk_rot_prepare` writes it -> fp32 [T, heads, vdim]: attention
     of every token over its own sequence's cache rows; the scaled scores of all heads are mixed by talk fp32 [heads, heads]
     (s'_h = sum_g talk[h, g] s_g) before the soft-max.  chunk > 0: a query sees only keys of its own chunk of `chunk` positions
-    (counted from position 0); window > 0: only the last `window` keys."""
-    _cuda(q, cache, talk)
+    (counted from position 0); window > 0: only the last `window` keys.  sink fp32 [heads]: exp(sink[h]) joins head h's soft-max
+    denominator (after the mix, not scaled) and carries no value."""
+    _cuda(q, cache, talk, sink)
     T, H, d = q.shape
     assert q.is_contiguous() and cache.is_contiguous() and q.dtype == torch.float32
     assert talk is None or (talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (H, H))
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.shape == (H,))
     out = torch.empty(T, H, vdim, dtype=torch.float32, device=q.device)
     lib = _lib.load_seq()
     need = ctypes.c_int64(0)
@@ -502,5 +509,93 @@ def talk_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, kv_head
     _lib.check_seq(lib.b200_seq_talk_attn(
         _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
         _ptr(step.seq_of_token), _ptr(step.cu_q), step.B, _ptr(step.position_ids), _ptr(talk), _ptr(out), T, H, kv_heads, d, vdim, int(chunk),
-        int(window), float(scale), cache.shape[1], _ptr(partial), nsplit, _stream()), "seq_talk_attn")
+        int(window), float(scale), cache.shape[1], _ptr(partial), nsplit, _ptr(sink), _stream()), "seq_talk_attn")
+    return out
+
+
+def streams_step(X: torch.Tensor, *, init: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                 out_coef: Optional[torch.Tensor] = None, in_coef: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                 eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """Several residual streams per token, X fp32 [T, S, W] in place; one launch does what lies between two sublayers.
+    init [T, W]: every stream starts as this row.  y [T, W] (+ mix [S, S] indexed [from, to], out_coef [S]): all streams at once
+    from the old ones, X_t <- sum_s mix[s, t] X_s + out_coef[t] y.  in_coef [S]: returns unit_rms(sum_s in_coef[s] X_s) * norm_w of
+    the new streams in norm_w's element type (norm_w None: the plain sum in `out_dtype`).  All coefficients fp32."""
+    _cuda(X, init, y, mix, out_coef, in_coef, norm_w)
+    assert X.dtype == torch.float32 and X.is_contiguous() and X.dim() == 3
+    T, S, W = X.shape
+    for t, shape in ((init, (T, W)), (y, (T, W)), (mix, (S, S)), (out_coef, (S,)), (in_coef, (S,))):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == shape)
+    dt = norm_w.dtype if norm_w is not None else (out_dtype or torch.float32)
+    typed = torch.empty(T, W, dtype=dt, device=X.device) if in_coef is not None else None
+    _lib.check_seq(_lib.load_seq().b200_seq_streams_step(_ptr(X), S, _ptr(init), _ptr(y), _ptr(mix), _ptr(out_coef), _ptr(in_coef), _ptr(norm_w),
+                                                         _dt(dt), _ptr(typed), T, W, float(eps), _stream()), "seq_streams_step")
+    return typed
+
+
+ACT_TANH = 2
+
+
+def ff_act(x: torch.Tensor, act: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(x) element by element (ACT_SILU, ACT_GELU_TANH, ACT_TANH), evaluated in fp32; x [T, F] may be a column slice; fp32 rows may
+    come out in another element type."""
+    _cuda(x)
+    assert x.dim() == 2 and x.stride(1) == 1
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_ff_act(_ptr(x), _dt(x), x.stride(0), _ptr(out), _dt(out), x.shape[0], x.shape[1], int(act), _stream()),
+                   "seq_ff_act")
+    return out
+
+
+def heads_turn_gate(a: torch.Tensor, gate: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int,
+                    interleaved: bool, step: RaggedStep, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None, out_scale: float = 1.0
+                    ) -> torch.Tensor:
+    """a fp32 [T, H, dv] -> [T, H * dv] in out_dtype: the first `rot` columns of every head turned back by the token's position (the
+    inverse of the values' turn in `qk_rot_prepare`), then the head times sigmoid(gate[t, h]) (gate fp32 [T, H], may be a column slice)
+    and times out_scale.  `out` may be a column slice of a wider buffer (the input of a product that several mixers share)."""
+    _cuda(a, gate, cos, sin)
+    T, H, dv = a.shape
+    assert a.dtype == torch.float32 and a.is_contiguous() and (gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, H)))
+    assert rot == 0 or (cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == rot // 2)
+    if out is None:
+        out = torch.empty(T, H * dv, dtype=out_dtype, device=a.device)
+    assert out.dtype == out_dtype and out.shape == (T, H * dv) and out.stride(1) == 1
+    _lib.check_seq(_lib.load_seq().b200_seq_heads_turn_gate(_ptr(a), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(cos), _ptr(sin),
+                                                            int(rot), int(interleaved), _ptr(step.position_ids), _ptr(out), _dt(out),
+                                                            out.stride(0), float(out_scale), T, H, dv, _stream()), "seq_heads_turn_gate")
+    return out
+
+
+def gdelta_scan(raw: torch.Tensor, col_r: int, col_k: int, col_v: int, col_a: int, dec: torch.Tensor, col_d: int, a_bias: torch.Tensor,
+                w0: torch.Tensor, decay_scale: float, S: torch.Tensor, step: RaggedStep, H: int, dk: int, dv: int) -> torch.Tensor:
+    """Generalised delta rule -> y fp32 [T, H * dv]; S fp32 [slots, H, dk, dv] advanced in place.  raw fp32: read vectors, keys and
+    removal logits (H x dk each) and values (H x dv) at the given columns; dec fp32: decay logits (H x dk) at col_d; per token
+    S <- diag(w) S - (a * u)(u^T S) + k v^T with u the unit-length key, w = exp(-decay_scale sigmoid(dec + w0)), a = sigmoid(. + a_bias)."""
+    _cuda(raw, dec, S, a_bias, w0)
+    assert raw.dtype == torch.float32 and dec.dtype == torch.float32 and S.dtype == torch.float32 and S.is_contiguous()
+    assert raw.stride(1) == 1 and dec.stride(1) == 1 and a_bias.dtype == w0.dtype and a_bias.is_contiguous() and w0.is_contiguous()
+    y = torch.empty(step.T, H * dv, dtype=torch.float32, device=raw.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_gdelta_scan(
+        _ptr(raw), raw.stride(0), col_r, col_k, col_v, col_a, _ptr(dec), dec.stride(0), col_d, _ptr(a_bias), _ptr(w0), _dt(w0), float(decay_scale),
+        _ptr(S), _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(y), y.stride(0), step.B, H, dk, dv, _stream()),
+        "seq_gdelta_scan")
+    return y
+
+
+def mingru_scan(proj: torch.Tensor, col_z: int, col_x: int, col_g: int, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor],
+                state: torch.Tensor, step: RaggedStep, width: int, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+                out_scale: float = 1.0) -> torch.Tensor:
+    """Minimal gated recurrent unit -> S_t * SiLU(gate) * out_scale [T, width] in out_dtype (col_g < 0: S_t), optionally into `out`, a
+    column slice of a wider buffer; state fp32 [slots, width] advanced in place.  proj fp32: update-gate logits, candidate inputs and output-gate logits at the given columns; z = sigmoid(. + z_bias),
+    candidate = x + 1/2 for x >= 0 and sigmoid(x) below, S <- (1 - z) S + z candidate."""
+    _cuda(proj, state, z_bias, x_bias)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    assert z_bias is None or x_bias is None or z_bias.dtype == x_bias.dtype
+    b = z_bias if z_bias is not None else x_bias
+    if out is None:
+        out = torch.empty(step.T, width, dtype=out_dtype, device=proj.device)
+    assert out.dtype == out_dtype and out.shape == (step.T, width) and out.stride(1) == 1
+    _lib.check_seq(_lib.load_seq().b200_seq_mingru_scan(
+        _ptr(proj), proj.stride(0), col_z, col_x, col_g, _ptr(z_bias), _ptr(x_bias), 1 if b is None else _dt(b), _ptr(state),
+        _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(out), _dt(out), out.stride(0), float(out_scale), step.B, width, _stream()),
+        "seq_mingru_scan")
     return out

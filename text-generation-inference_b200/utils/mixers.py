@@ -148,9 +148,12 @@ class MLSTMMixer(nn.Module):
     q scaled by dim^-1/2, per-head unit-RMS, weight, sigmoid output gate, out-projection.  State fp32.
     Tensors under `prefix`: q, k, v, g, i, i.b, f, f.b, norm, o."""
 
-    def __init__(self, prefix: str, weights, *, heads: int, dim: int, vdim: int, gate_cap: float, eps: float):
+    def __init__(self, prefix: str, weights, *, heads: int, dim: int, vdim: int, gate_cap: float, eps: float,
+                 out_dtype: Optional[torch.dtype] = None):
+        """`out_dtype`: element type of the result (None: the projections' type; torch.float32 for a stream that adds it in fp32)"""
         super().__init__()
         _need_single_rank(weights, "MLSTMMixer")
+        self.out_dtype = out_dtype
         self.H, self.d, self.dv, self.cap, self.eps = heads, dim, vdim, float(gate_cap), float(eps)
         get = lambda n: weights.get_tensor(f"{prefix}.{n}").contiguous()  # noqa: E731
         self.w_in = torch.cat([get("q"), get("k"), get("v"), get("g"), get("i"), get("f")], 0).contiguous()
@@ -168,7 +171,7 @@ class MLSTMMixer(nn.Module):
                            store["m"], step, H, d, dv)
         gated = ops.group_rmsnorm_gate(y, self.norm_w, H, self.eps, self.dtype, gate=proj[:, qk + H * dv:qk + vg],
                                        gate_kind=ops.GATE_SIGMOID_AFTER)
-        return ops.linear(gated, self.w_o)
+        return ops.linear(gated, self.w_o, out_dtype=self.out_dtype)
 
 
 class ClampedGatedMLP(nn.Module):
@@ -449,3 +452,219 @@ class TalkingHeadsAttention(nn.Module):
                           chunk=self.chunk, window=self.window)
         o = ops.cast_rows(a.view(step.T, self.H * self.dv), self.dtype)
         return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+class SinkRotaryAttention(nn.Module):
+    """Grouped-query attention over a sliding window with a learned sink logit per head in the soft-max denominator (the sink has
+    no key and no value: it only takes weight), a sigmoid gate per head on the result, and values that carry their position:
+    a value is turned over `value_rotary.dims` of its columns by its own position before it is cached, and every head's result
+    is turned back by the query's position, so the result only sees position differences.  Before that: an optional depth-wise
+    causal convolution (`conv` taps, no bias, no activation) after each of the q / k / v projections, an RMS norm over the whole q
+    and the whole k projection (a weight per column), rotation of the first `rotary.dims` columns of every q / k head (column i
+    with column i + dims / 2).  Cached per token: rotated keys and turned values of all key heads (token-major row); per
+    sequence: the last conv - 1 projected rows (fp32).
+    A mixer that can share its input and output products with a neighbour: `in_rows()` are the rows it adds to the input
+    projection, `from_projection` continues from the fp32 projection and leaves the gated heads, times `out_scale`, in `out`;
+    `w_o` finishes.
+    Tensors under `prefix`: q, k, v, [q.conv, k.conv, v.conv,] q.norm, k.norm, [sink,] [g,] o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, rotary: Optional[ScaledRotaryTables],
+                 value_rotary: Optional[ScaledRotaryTables], value_pairs: str = "halves", conv: int = 0, window: Optional[int] = None,
+                 sink: bool = True, head_gate: bool = True, eps: float = 1e-6):
+        super().__init__()
+        _need_single_rank(weights, "SinkRotaryAttention")
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if value_pairs not in ("halves", "interleaved"):
+            raise ValueError("value_pairs is 'halves' or 'interleaved'")
+        self.H, self.G, self.d, self.dv, self.taps = int(heads), int(kv_heads), int(dim), int(vdim), int(conv or 0)
+        self.scale, self.rotary, self.value_rotary, self.window, self.eps = float(scale), rotary, value_rotary, int(window or 0), float(eps)
+        self.value_interleaved = value_pairs == "interleaved"
+        if rotary is not None and rotary.dims > dim:
+            raise ValueError("rotary dims exceed the head size")
+        if value_rotary is not None and value_rotary.dims > vdim:
+            raise ValueError("turned value columns exceed the value size")
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.cq, self.ck, self.cv = self.H * self.d, self.G * self.d, self.G * self.dv
+        self.channels = self.cq + self.ck + self.cv
+        self.w_in = torch.cat([get(n) for n in (("q", "k", "v", "g") if head_gate else ("q", "k", "v"))], 0).contiguous()
+        self.n_in = self.channels + (self.H if head_gate else 0)
+        self.head_gate = bool(head_gate)
+        self.conv_w = torch.cat([get(f"{n}.conv") for n in ("q", "k", "v")], 0).contiguous() if self.taps > 1 else None
+        self.q_norm, self.k_norm = get("q.norm").contiguous(), get("k.norm").contiguous()
+        self.sink = get("sink").float().contiguous() if sink else None
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        self.n_out = self.H * self.dv
+        if self.w_in.shape[0] != self.n_in or (self.conv_w is not None and self.conv_w.shape != (self.channels, self.taps)) or \
+                self.w_o.shape[1] != self.n_out or (self.sink is not None and self.sink.shape != (self.H,)):
+            raise ValueError(f"{prefix}: tensor shapes do not match the head sizes")
+
+    def in_rows(self) -> torch.Tensor:
+        return self.w_in
+
+    def cache_spec(self) -> LayerCacheSpec:
+        state = {"conv": (self.taps - 1, self.channels)} if self.taps > 1 else {}
+        return LayerCacheSpec(kind="paged", row_width=self.ck + self.cv, state=state)
+
+    def prepare_positions(self, n_pos: int, device) -> None:
+        for r in (self.rotary, self.value_rotary):
+            if r is not None:
+                r.tables(n_pos, device)
+
+    def from_projection(self, u: torch.Tensor, col0: int, step: ops.RaggedStep, pages: torch.Tensor, state, max_s: int, out: torch.Tensor,
+                        out_scale: float = 1.0) -> None:
+        """u fp32 [T, >= col0 + n_in]: this mixer's input projection from column col0 -> out [T, heads * vdim] (a column slice is fine)"""
+        c, cq = u, col0
+        if self.conv_w is not None:
+            c, cq = ops.causal_conv(u, col0, self.channels, self.conv_w, None, state["conv"], step), 0
+        cos, sin = self.rotary.tables(max_s, u.device) if self.rotary is not None else (None, None)
+        vr = self.value_rotary
+        vcos, vsin = vr.tables(max_s, u.device) if vr is not None else (None, None)
+        q = ops.qk_rot_prepare(c, col_q=cq, col_k=cq + self.cq, col_v=cq + self.cq + self.ck, heads=self.H, kv_heads=self.G, dim=self.d,
+                               vdim=self.dv, q_norm_w=self.q_norm, k_norm_w=self.k_norm, whole_norm=True, eps=self.eps, cos=cos, sin=sin,
+                               rot=self.rotary.dims if self.rotary is not None else 0, step=step, cache=pages, k_off=0, v_off=self.ck,
+                               v_cos=vcos, v_sin=vsin, v_rot=vr.dims if vr is not None else 0, v_interleaved=self.value_interleaved)
+        a = ops.talk_attn(q, pages, step, kv_heads=self.G, vdim=self.dv, k_off=0, v_off=self.ck, scale=self.scale, window=self.window,
+                          sink=self.sink)
+        gate = u[:, col0 + self.channels:col0 + self.channels + self.H] if self.head_gate else None
+        ops.heads_turn_gate(a, gate, vcos, vsin, vr.dims if vr is not None else 0, self.value_interleaved, step, self.dtype, out=out,
+                            out_scale=out_scale)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages: torch.Tensor, state, max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        o = torch.empty(step.T, self.n_out, dtype=self.dtype, device=h.device)
+        self.from_projection(u, 0, step, pages, state, max_s, o)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+class MinGRUMixer(nn.Module):
+    """Minimal gated recurrent unit: per channel S <- (1 - z) S + z c, the gates reading only the current token:
+    z = sigmoid(W_z h + b_z), c = g(W_x h + b_x) with g(u) = u + 1/2 for u >= 0 and sigmoid(u) below; the result is
+    W_o (S * SiLU(W_g h)).  State per sequence: S [width] in fp32.  Shares products with a neighbour like `SinkRotaryAttention`.
+    Tensors under `prefix`: z, z.b, x, x.b, g, o."""
+
+    def __init__(self, prefix: str, weights, *, width: int):
+        super().__init__()
+        _need_single_rank(weights, "MinGRUMixer")
+        self.C = int(width)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_in = torch.cat([get("z"), get("x"), get("g")], 0).contiguous()
+        self.z_b, self.x_b = get("z.b").contiguous(), get("x.b").contiguous()
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        self.n_in, self.n_out = 3 * self.C, self.C
+        if self.w_in.shape[0] != self.n_in or self.w_o.shape[1] != self.C:
+            raise ValueError(f"{prefix}: projection shapes do not match the width")
+
+    def in_rows(self) -> torch.Tensor:
+        return self.w_in
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state={"S": (self.C,)})
+
+    def from_projection(self, u: torch.Tensor, col0: int, step: ops.RaggedStep, pages, state, max_s: int, out: torch.Tensor,
+                        out_scale: float = 1.0) -> None:
+        C = self.C
+        ops.mingru_scan(u, col0, col0 + C, col0 + 2 * C, self.z_b, self.x_b, state["S"], step, C, self.dtype, out=out, out_scale=out_scale)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages, state, max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        o = torch.empty(step.T, self.C, dtype=self.dtype, device=h.device)
+        self.from_projection(u, 0, step, pages, state, max_s, o)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+class ParallelMixers(nn.Module):
+    """Two mixers side by side that read the same input: left_scale * left(h) + right_scale * right(h).  Both must offer
+    `in_rows` / `from_projection` / `w_o` / `n_in` / `n_out`: their input projections run as ONE product, each leaves what its
+    output projection reads - times its scale, before the rounding to the projections' element type - in its columns of one
+    buffer, and ONE product over [left | right] columns adds the two results.  At most one of them keeps paged rows; the state
+    tensors of both live in the layer's slot under `left.` / `right.` names."""
+
+    def __init__(self, left: nn.Module, right: nn.Module, left_scale: float, right_scale: float):
+        super().__init__()
+        self.left, self.right, self.ls, self.rs = left, right, float(left_scale), float(right_scale)
+        self.w_in = torch.cat([left.in_rows(), right.in_rows()], 0).contiguous()
+        self.w_o = torch.cat([left.w_o, right.w_o], 1).contiguous()
+        self.dtype = self.w_o.dtype
+        sl, sr = left.cache_spec(), right.cache_spec()
+        if sl.kind == "paged" and sr.kind == "paged":
+            raise NotImplementedError("two paged mixers in one layer")
+        self._spec = LayerCacheSpec(kind="paged" if "paged" in (sl.kind, sr.kind) else "state", row_width=max(sl.row_width, sr.row_width),
+                                    state={**{f"left.{k}": v for k, v in (sl.state or {}).items()},
+                                           **{f"right.{k}": v for k, v in (sr.state or {}).items()}})
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return self._spec
+
+    def prepare_positions(self, n_pos: int, device) -> None:
+        for m in (self.left, self.right):
+            if hasattr(m, "prepare_positions"):
+                m.prepare_positions(n_pos, device)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages, state: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        L, R = self.left, self.right
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        o = torch.empty(step.T, L.n_out + R.n_out, dtype=self.dtype, device=h.device)
+        side = lambda p: {k[len(p):]: v for k, v in (state or {}).items() if k.startswith(p)}  # noqa: E731
+        L.from_projection(u, 0, step, pages, side("left."), max_s, o[:, :L.n_out], self.ls)
+        R.from_projection(u, L.n_in, step, pages, side("right."), max_s, o[:, L.n_out:], self.rs)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+class GeneralDeltaMixer(nn.Module):
+    """Generalised delta rule: per head a [dim, dim] memory S in fp32; every token, with the unit-length key u,
+    S <- diag(w) S - (a * u)(u^T S) + k v^T (decay and removal both read the old memory), o = S^T r.  The decay per head and key
+    channel comes from a low-rank projection, w = exp(-decay_scale * sigmoid(W_w2 tanh(W_w1 h) + w0)), the removal rate is
+    a = sigmoid(W_a h + b_a).  Each head's o is divided by its RMS, times a weight per column, times sigmoid(W_g h); then the
+    output projection.  State per sequence: S in fp32.
+    Tensors under `prefix`: r, k, v, g, a, a.b, w1, w2, w0, norm, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, dim: int, eps: float, decay_scale: float = math.exp(-0.5)):
+        super().__init__()
+        _need_single_rank(weights, "GeneralDeltaMixer")
+        self.H, self.d, self.eps, self.decay_scale = int(heads), int(dim), float(eps), float(decay_scale)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.n = self.H * self.d
+        self.w_in = torch.cat([get(n) for n in ("r", "k", "v", "g", "a", "w1")], 0).contiguous()    # -> [r | k | v | gate | removal | low rank]
+        self.rank = get("w1").shape[0]
+        self.w2 = get("w2").contiguous()
+        self.a_b, self.w0, self.norm_w = get("a.b").contiguous(), get("w0").contiguous(), get("norm").contiguous()
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        if self.w_in.shape[0] != 5 * self.n + self.rank or self.w2.shape != (self.n, self.rank) or self.norm_w.shape != (self.n,):
+            raise ValueError(f"{prefix}: projection shapes do not match the head sizes")
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state={"S": (self.H, self.d, self.d)})
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages, state: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        """-> fp32 [T, width]"""
+        n = self.n
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        low = ops.ff_act(u[:, 5 * n:5 * n + self.rank], ops.ACT_TANH, out_dtype=self.dtype)
+        dec = ops.linear(low, self.w2, out_dtype=torch.float32)
+        y = ops.gdelta_scan(u, 0, n, 2 * n, 4 * n, dec, 0, self.a_b, self.w0, self.decay_scale, state["S"], step, self.H, self.d, self.d)
+        gated = ops.group_rmsnorm_gate(y, self.norm_w, self.H, self.eps, self.dtype, gate=u[:, 3 * n:4 * n], gate_kind=ops.GATE_SIGMOID_AFTER)
+        return ops.linear(gated, self.w_o, out_dtype=torch.float32)
+
+
+class PlainMLP(nn.Module):
+    """down(act(up x)) with act SiLU or the tanh form of GELU, no gate, no biases.  The result is fp32.
+    Tensors under `prefix`: up, down."""
+
+    def __init__(self, prefix: str, weights, *, activation: str):
+        super().__init__()
+        _need_single_rank(weights, "PlainMLP")
+        if activation not in ("silu", "gelu_tanh"):
+            raise NotImplementedError(f"activation {activation!r}")
+        self.act = ops.ACT_SILU if activation == "silu" else ops.ACT_GELU_TANH
+        self.w_up = weights.get_tensor(f"{prefix}.up").contiguous()
+        self.w_down = weights.get_tensor(f"{prefix}.down").contiguous()
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.linear(ops.ff_act(ops.linear(h, self.w_up), self.act), self.w_down, out_dtype=torch.float32)
