@@ -78,6 +78,17 @@ def turn_halves(x, positions, dims: int, base: float, sign: float = 1.0):
     return torch.cat([a * c - b * s, b * c + a * s, x[..., dims:]], -1)
 
 
+def turn_neighbours(x, positions, dims: int, base: float, sign: float = 1.0):
+    """as turn_halves with columns 2i and 2i + 1 as pair i (the model does not use it; the kernels offer both layouts)"""
+    i = torch.arange(dims // 2, dtype=x.dtype)
+    ang = sign * positions.to(x.dtype)[:, None] * base ** (-2.0 * i / dims)[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = x[..., 0:dims:2], x[..., 1:dims:2]
+    out = x.clone()
+    out[..., 0:dims:2], out[..., 1:dims:2] = a * c - b * s, b * c + a * s
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ mixers
 def sink_window_attention(h, p, m: dict, eps: float):
     """h [L, W] -> [L, W]: the attention half of the parallel mixer"""
@@ -89,11 +100,10 @@ def sink_window_attention(h, p, m: dict, eps: float):
     q = (unit_rms(q, eps) * p["q.norm"]).view(L, H, d)
     k = (unit_rms(k, eps) * p["k.norm"]).view(L, G, d)
     v = v.view(L, G, dv)
-    base = 10000.0
-    if m.get("rot"):
-        base = float(m["rot"]["base"])
-        q, k = turn_halves(q, pos, int(m["rot"]["dims"]), base), turn_halves(k, pos, int(m["rot"]["dims"]), base)
-    v = turn_halves(v, pos, dv, base)                                  # every value column turns with the value's position
+    rot = m.get("rot")
+    if rot:
+        q, k = turn_halves(q, pos, int(rot["dims"]), float(rot["base"])), turn_halves(k, pos, int(rot["dims"]), float(rot["base"]))
+        v = turn_halves(v, pos, dv, float(rot["base"]))                # every value column turns with the value's position
     rep = H // G
     s = torch.einsum("ihd,jhd->hij", q, k.repeat_interleave(rep, dim=1)) * float(m["scale"])
     see = pos[None, :] <= pos[:, None]
@@ -103,7 +113,8 @@ def sink_window_attention(h, p, m: dict, eps: float):
     sink = p["sink"][:, None, None].expand(H, L, 1) if "sink" in p else s.new_full((H, L, 1), float("-inf"))
     a = torch.softmax(torch.cat([s, sink], -1), -1)[..., :L]           # the sink takes weight and gives nothing
     o = torch.einsum("hij,jhv->ihv", a, v.repeat_interleave(rep, dim=1))
-    o = turn_halves(o, pos, dv, base, sign=-1.0)                       # back by the query's position
+    if rot:
+        o = turn_halves(o, pos, dv, float(rot["base"]), sign=-1.0)     # back by the query's position
     o = o * torch.sigmoid(h @ p["g"].T)[:, :, None]
     return o.reshape(L, H * dv) @ p["o"].T
 
@@ -179,12 +190,14 @@ def silu_expert(h, p, prefix: str):
 
 def routed_experts(h, p, f: dict, margins: Optional[list] = None):
     """soft-max scores over all experts; the `top` largest are picked and weighted by score / (sum of the picked scores + 1e-20).
-    `margins`, when a list, receives per row the gap in score between the last pick and the best expert left out"""
+    `margins`, when a list, receives per row the gap in router logit between the last pick and the best expert left out"""
     E, top = int(f["router"]["experts"]), int(f["router"]["top"])
-    s = torch.softmax(h @ p["router"].T, -1)
+    z = h @ p["router"].T
+    s = torch.softmax(z, -1)
     val, idx = torch.topk(s, top, dim=-1)
     if margins is not None:
-        margins.append(val[:, -1] - torch.topk(s, top + 1, dim=-1).values[:, -1] if top < E else torch.full_like(val[:, 0], float("inf")))
+        zs = torch.topk(z, min(top + 1, E), dim=-1).values
+        margins.append(zs[:, top - 1] - zs[:, top] if top < E else torch.full_like(val[:, 0], float("inf")))
     wgt = val / (val.sum(-1, keepdim=True) + 1e-20)
     out = torch.zeros(h.shape[0], p["e0.down"].shape[0], dtype=h.dtype)
     for e in range(E):
@@ -229,3 +242,107 @@ def forward(config: dict, sd: Dict[str, torch.Tensor], tokens: List[int], dtype=
         if residuals is not None:
             residuals.append(X.sum(0))
     return (unit_rms(X.sum(0), eps) * sd["final.norm"]) @ sd["embed"].T
+
+
+# ------------------------------------------------------------------------------------------------ random models
+def random_config(*, width: int = 40, vocab: int = 72, order=("parallel", "mlstm", "general_delta", "parallel"), loop=(1, 3, 2), streams=3,
+                  residual_mult: float = 0.7, heads: int = 6, kv_heads: int = 2, dim: int = 10, vdim: int = 12, rot_dims=6, base: float = 100.0,
+                  window=20, conv=3, sharp: float = 1.0, gru_width: int = 28, left_scale: float = 0.8, right_scale: float = 0.6,
+                  m_heads: int = 3, m_dim: int = 6, m_vdim: int = 10, gate_cap: float = 9.0, d_heads: int = 2, d_dim: int = 12,
+                  mlp=("dense", "moe", "moe", None), experts: int = 5, top: int = 2, ff: int = 24, eps: float = 1e-5) -> dict:
+    """a small configuration; `loop` = (start, stop, times) or None, `streams` None for a single plain stream, `rot_dims` / `window` /
+    `conv` None to leave the entry out, `sharp` multiplies the attention's score scale"""
+    layers = []
+    for i, kind in enumerate(order):
+        if kind == "parallel":
+            left = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "vdim": vdim, "scale": dim ** -0.5 * sharp}
+            if conv:
+                left["conv"] = conv
+            if rot_dims:
+                left["rot"] = {"base": base, "dims": rot_dims}
+            if window:
+                left["mask"] = {"size": window}
+            mixer = {"left": left, "left_scale": left_scale, "right": {"width": gru_width}, "right_scale": right_scale}
+        elif kind == "mlstm":
+            mixer = {"dim": m_dim, "gate_cap": gate_cap, "heads": m_heads, "vdim": m_vdim}
+        else:
+            mixer = {"dim": d_dim, "heads": d_heads}
+        f = mlp[i]
+        if f == "dense":
+            f = {"kind": "dense", "ff": ff + 4}
+        elif f == "moe":
+            f = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": f})
+    out = {"architecture": "Nasozen", "layers": layers, "norm": {"eps": eps}, "residual_mult": residual_mult, "vocab": vocab, "width": width}
+    if streams:
+        out["streams"] = streams
+    if loop:
+        out["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return out
+
+
+def tensor_shapes(config: dict, decay_rank: int = 5) -> Dict[str, tuple]:
+    W, V = int(config["width"]), int(config["vocab"])
+    S = int(config["streams"]) if config.get("streams") else 0
+    out = {"embed": (V, W), "final.norm": (W,)}
+    for i, layer in enumerate(config["layers"]):
+        m, pre = layer["mixer"], f"l{i}.mix."
+        if layer["type"] == "parallel":
+            a, C = m["left"], m["right"]["width"]
+            H, G, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            mix = {"left.q": (H * d, W), "left.k": (G * d, W), "left.v": (G * dv, W), "left.q.norm": (H * d,), "left.k.norm": (G * d,),
+                   "left.sink": (H,), "left.g": (H, W), "left.o": (W, H * dv)}
+            if a.get("conv"):
+                mix.update({"left.q.conv": (H * d, a["conv"]), "left.k.conv": (G * d, a["conv"]), "left.v.conv": (G * dv, a["conv"])})
+            mix.update({"right.z": (C, W), "right.z.b": (C,), "right.x": (C, W), "right.x.b": (C,), "right.g": (C, W), "right.o": (W, C)})
+        elif layer["type"] == "mlstm":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            mix = {"q": (H * d, W), "k": (H * d, W), "v": (H * dv, W), "g": (H * dv, W), "i": (H, W), "i.b": (H,), "f": (H, W), "f.b": (H,),
+                   "norm": (H * dv,), "o": (W, H * dv)}
+        else:
+            n = m["heads"] * m["dim"]
+            mix = {"r": (n, W), "k": (n, W), "v": (n, W), "g": (n, W), "a": (n, W), "a.b": (n,), "w1": (decay_rank, W), "w2": (n, decay_rank),
+                   "w0": (n,), "norm": (n,), "o": (W, n)}
+        out.update({pre + k: v for k, v in mix.items()})
+        subs = [1] + ([2] if layer.get("mlp") else [])
+        for q in subs:
+            out[f"l{i}.norm{q}"] = (W,)
+            if S:
+                out.update({f"l{i}.hc{q}.in": (S,), f"l{i}.hc{q}.out": (S,), f"l{i}.hc{q}.mix": (S, S)})
+        f = layer.get("mlp")
+        if f and f["kind"] == "dense":
+            out.update({f"l{i}.mlp.up": (int(f["ff"]), W), f"l{i}.mlp.down": (W, int(f["ff"]))})
+        elif f:
+            E, n = int(f["router"]["experts"]), int(f["expert"]["ff"])
+            out[f"l{i}.mlp.router"] = (E, W)
+            for e in range(E):
+                out.update({f"l{i}.mlp.e{e}.gate": (n, W), f"l{i}.mlp.e{e}.up": (n, W), f"l{i}.mlp.e{e}.down": (W, n)})
+    return out
+
+
+def random_state_dict(config: dict, seed: int = 0, decay_rank: int = 5) -> Dict[str, torch.Tensor]:
+    """weights that are exactly representable in bfloat16, so that every element type starts from the same numbers"""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in tensor_shapes(config, decay_rank).items():
+        parts = name.split(".")
+        leaf = parts[-1]
+        if ".hc" in name:
+            S = shape[0]
+            t = {"in": torch.full(shape, 1.0 / S), "out": torch.ones(shape), "mix": torch.eye(S)}[leaf] + torch.randn(shape, generator=g) * 0.25
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g) * 0.6
+        elif leaf == "sink":
+            t = torch.randn(shape, generator=g) * 1.5
+        elif leaf == "w0":
+            t = torch.randn(shape, generator=g) * 1.5
+        elif leaf == "b":
+            t = torch.randn(shape, generator=g) * (2.0 if parts[-2] in ("i", "f") else 0.7)
+        elif leaf == "w2":
+            t = torch.randn(shape, generator=g) * 1.2
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) * ((0.7 if name == "embed" else 1.5 / math.sqrt(shape[1])))
+        else:  # norm weights
+            t = 1.0 + torch.randn(shape, generator=g) * 0.3
+        sd[name] = t.to(torch.bfloat16).to(torch.float32)
+    return sd

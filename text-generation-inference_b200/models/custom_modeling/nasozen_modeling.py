@@ -102,7 +102,7 @@ def tensor_shapes(raw: Dict[str, Any], decay_rank: int = 16) -> Dict[str, tuple]
                    "left.sink": (H,), "left.g": (H, W), "left.o": (W, H * dv), "right.z": (C, W), "right.z.b": (C,), "right.x": (C, W),
                    "right.x.b": (C,), "right.g": (C, W), "right.o": (W, C)}
             taps = int(a.get("conv") or 0)
-            if taps > 1:
+            if taps >= 1:
                 mix.update({"left.q.conv": (H * d, taps), "left.k.conv": (G * d, taps), "left.v.conv": (G * dv, taps)})
         elif layer["type"] == "mlstm":
             H, d, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])

@@ -490,7 +490,7 @@ class SinkRotaryAttention(nn.Module):
         self.w_in = torch.cat([get(n) for n in (("q", "k", "v", "g") if head_gate else ("q", "k", "v"))], 0).contiguous()
         self.n_in = self.channels + (self.H if head_gate else 0)
         self.head_gate = bool(head_gate)
-        self.conv_w = torch.cat([get(f"{n}.conv") for n in ("q", "k", "v")], 0).contiguous() if self.taps > 1 else None
+        self.conv_w = torch.cat([get(f"{n}.conv") for n in ("q", "k", "v")], 0).contiguous() if self.taps >= 1 else None
         self.q_norm, self.k_norm = get("q.norm").contiguous(), get("k.norm").contiguous()
         self.sink = get("sink").float().contiguous() if sink else None
         self.w_o = get("o").contiguous()
@@ -504,7 +504,7 @@ class SinkRotaryAttention(nn.Module):
         return self.w_in
 
     def cache_spec(self) -> LayerCacheSpec:
-        state = {"conv": (self.taps - 1, self.channels)} if self.taps > 1 else {}
+        state = {"conv": (max(self.taps - 1, 1), self.channels)} if self.taps >= 1 else {}   # a single tap is a weight per channel
         return LayerCacheSpec(kind="paged", row_width=self.ck + self.cv, state=state)
 
     def prepare_positions(self, n_pos: int, device) -> None:
