@@ -1141,6 +1141,45 @@ def _stream_family_measure(raw, cfg, op_names, PB, PL, DB, DL, K, Wm, timed, lib
             "picked": picked}
 
 
+def _noganex_side(width, env):
+    """the Noganex half of --noganex-compare (also the partner of --nasozen-compare) -> its result entry"""
+    from tgis_b200.models.custom_modeling import noganex_modeling
+    from tgis_b200.utils.synthetic import noganex_config
+    PB, PL, DB, DL, K, Wm, ctx = (env[k] for k in ("PB", "PL", "DB", "DL", "K", "Wm", "ctx"))
+    timed, lib, hbm, tens, common, us = (env[k] for k in ("timed", "lib", "hbm", "tens", "common", "us"))
+    raw = noganex_config(f"noganex-w{width}")
+    names = ["linear", "embed_scale", "cast_rows", "rmsnorm_rows", "gated_rms_add", "causal_conv", "delta_scan", "qk_rot_prepare", "talk_attn",
+             "group_rmsnorm_gate", "moe_route", "moe_gather_rows", "moe_linear", "ff_gate", "moe_combine_add"]
+    r = _stream_family_measure(raw, noganex_modeling.NoganexConfig(raw), names, PB, PL, DB, DL, K, Wm, timed, lib)
+    shapes = noganex_modeling.tensor_shapes(raw)
+    attn = [l["mixer"] for l in raw["layers"] if l["type"] == "attention"]
+    delta = [l["mixer"] for l in raw["layers"] if l["type"] == "delta"]
+    attn_flops = sum(PB * (PL * (PL + 1) // 2) * m["heads"] * (m["dim"] + m["vdim"] + m["heads"]) * 2 for m in attn)
+    attn_row = sum(m["kv_heads"] * (m["dim"] + m["vdim"]) for m in attn)       # elements a decoding token reads per cached token
+    state_b = sum(m["heads"] * m["dim"] * m["vdim"] * 4 * 2 for m in delta)    # state read + written per sequence and step
+    moes = [l["mlp"] for l in raw["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe"]
+    expert_w = 3 * width * moes[0]["expert"]["ff"]
+    top = moes[0]["router"]["top"]
+    dense_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1] if ".mlp.e" not in n and n not in ("embed", "head"))
+    head_w = shapes["head"][0] * shapes["head"][1]
+    lin_flops = 2 * PB * PL * (dense_w + len(moes) * top * expert_w) + 2 * PB * head_w
+    a_us, s_us, m_us = us(r["dec_k"], "talk_attn"), us(r["dec_k"], "delta_scan"), r["dec_k"].get("moe_linear_mma_kernel", 0.0)
+    g_us = r["dec_k"].get("gemm_f16_kernel", 0.0)
+    kernels = {
+        "talk_attn prefill": {"ms": r["pre_ops"]["talk_attn"], "tflops": attn_flops / r["pre_ops"]["talk_attn"] / 1e9,
+                              "of_measured_tensor": attn_flops / (r["pre_ops"]["talk_attn"] * 1e-3) / tens},
+        "talk_attn decode": {"us": a_us, "of_measured_hbm": DB * ctx * attn_row * 2 / (max(a_us, 1e-9) * 1e-6) / hbm},
+        "delta_scan prefill": {"ms": r["pre_ops"]["delta_scan"], "tokens_per_s_per_layer": PB * PL * len(delta) / (r["pre_ops"]["delta_scan"] * 1e-3)},
+        "delta_scan decode": {"us": s_us, "of_measured_hbm": DB * state_b / (max(s_us, 1e-9) * 1e-6) / hbm},
+        "linear prefill (projections, gates, one product per expert)": {"ms": r["pre_ops"]["linear"],
+                                                                        "of_measured_tensor": lin_flops / (r["pre_ops"]["linear"] * 1e-3) / tens},
+        "moe_linear decode (grouped, picked experts' weights once)": {"us": m_us, "experts_picked_all_layers": r["picked"], "of_measured_hbm":
+                                                                      r["picked"] * expert_w * 2 / (max(m_us, 1e-9) * 1e-6) / hbm},
+        "linear decode (tcgen05 projections)": {"us": g_us, "of_measured_hbm": (dense_w + head_w) * 2 / (max(g_us, 1e-9) * 1e-6) / hbm},
+    }
+    return common(f"noganex-w{width}", raw, r, kernels, {"experts": moes[0]["router"]["experts"], "top": top})
+
+
 def run_noganex_compare(args):
     """Noganex (bfloat16) beside Dubesun (bfloat16), the closest family of the engine (fp32 stream, attention over a paged cache, short
     convolutions, routed experts), at equal width and depth on random weights: prefill of 4 x 1024 tokens and decode of 32 sequences at
@@ -1149,8 +1188,8 @@ def run_noganex_compare(args):
     import torch
     import tgis_b200  # noqa: F401
     from tgis_b200 import _lib as _libmod
-    from tgis_b200.models.custom_modeling import dubesun_modeling, noganex_modeling
-    from tgis_b200.utils.synthetic import dubesun_config, noganex_config
+    from tgis_b200.models.custom_modeling import dubesun_modeling
+    from tgis_b200.utils.synthetic import dubesun_config
 
     pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
     if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
@@ -1194,39 +1233,9 @@ def run_noganex_compare(args):
         return sum(v for k, v in dec_k.items() if k.startswith(prefixes))
 
     widths = (2048, 4096) if not args.layers else (2048,)
+    env = dict(PB=PB, PL=PL, DB=DB, DL=DL, K=K, Wm=Wm, ctx=ctx, timed=timed, lib=lib, hbm=hbm, tens=tens, common=common, us=us)
     for width in widths:
-        # ---------------------------------------------------------------- Noganex
-        raw = noganex_config(f"noganex-w{width}")
-        names = ["linear", "embed_scale", "cast_rows", "rmsnorm_rows", "gated_rms_add", "causal_conv", "delta_scan", "qk_rot_prepare", "talk_attn",
-                 "group_rmsnorm_gate", "moe_route", "moe_gather_rows", "moe_linear", "ff_gate", "moe_combine_add"]
-        r = _stream_family_measure(raw, noganex_modeling.NoganexConfig(raw), names, PB, PL, DB, DL, K, Wm, timed, lib)
-        shapes = noganex_modeling.tensor_shapes(raw)
-        attn = [l["mixer"] for l in raw["layers"] if l["type"] == "attention"]
-        delta = [l["mixer"] for l in raw["layers"] if l["type"] == "delta"]
-        attn_flops = sum(PB * (PL * (PL + 1) // 2) * m["heads"] * (m["dim"] + m["vdim"] + m["heads"]) * 2 for m in attn)
-        attn_row = sum(m["kv_heads"] * (m["dim"] + m["vdim"]) for m in attn)       # elements a decoding token reads per cached token
-        state_b = sum(m["heads"] * m["dim"] * m["vdim"] * 4 * 2 for m in delta)    # state read + written per sequence and step
-        moes = [l["mlp"] for l in raw["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe"]
-        expert_w = 3 * width * moes[0]["expert"]["ff"]
-        top = moes[0]["router"]["top"]
-        dense_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1] if ".mlp.e" not in n and n not in ("embed", "head"))
-        head_w = shapes["head"][0] * shapes["head"][1]
-        lin_flops = 2 * PB * PL * (dense_w + len(moes) * top * expert_w) + 2 * PB * head_w
-        a_us, s_us, m_us = us(r["dec_k"], "talk_attn"), us(r["dec_k"], "delta_scan"), r["dec_k"].get("moe_linear_mma_kernel", 0.0)
-        g_us = r["dec_k"].get("gemm_f16_kernel", 0.0)
-        kernels = {
-            "talk_attn prefill": {"ms": r["pre_ops"]["talk_attn"], "tflops": attn_flops / r["pre_ops"]["talk_attn"] / 1e9,
-                                  "of_measured_tensor": attn_flops / (r["pre_ops"]["talk_attn"] * 1e-3) / tens},
-            "talk_attn decode": {"us": a_us, "of_measured_hbm": DB * ctx * attn_row * 2 / (max(a_us, 1e-9) * 1e-6) / hbm},
-            "delta_scan prefill": {"ms": r["pre_ops"]["delta_scan"], "tokens_per_s_per_layer": PB * PL * len(delta) / (r["pre_ops"]["delta_scan"] * 1e-3)},
-            "delta_scan decode": {"us": s_us, "of_measured_hbm": DB * state_b / (max(s_us, 1e-9) * 1e-6) / hbm},
-            "linear prefill (projections, gates, one product per expert)": {"ms": r["pre_ops"]["linear"],
-                                                                            "of_measured_tensor": lin_flops / (r["pre_ops"]["linear"] * 1e-3) / tens},
-            "moe_linear decode (grouped, picked experts' weights once)": {"us": m_us, "experts_picked_all_layers": r["picked"], "of_measured_hbm":
-                                                                          r["picked"] * expert_w * 2 / (max(m_us, 1e-9) * 1e-6) / hbm},
-            "linear decode (tcgen05 projections)": {"us": g_us, "of_measured_hbm": (dense_w + head_w) * 2 / (max(g_us, 1e-9) * 1e-6) / hbm},
-        }
-        results.append(common(f"noganex-w{width}", raw, r, kernels, {"experts": moes[0]["router"]["experts"], "top": top}))
+        results.append(_noganex_side(width, env))
         # ---------------------------------------------------------------- Dubesun, the partner
         raw = dubesun_config(f"dubesun-w{width}")
         names = ["linear", "embed_add_pos", "rmsnorm_rows", "causal_conv", "heads_prepare", "paged_attn", "diff_combine", "group_rmsnorm_gate",
@@ -1263,6 +1272,116 @@ def run_noganex_compare(args):
     return 0
 
 
+def run_nasozen_compare(args):
+    """Nasozen (bfloat16) beside Noganex (bfloat16), the closest family of the engine (fp32 stream, whole-projection q / k norm and
+    rotate-half rotation in front of the same attention kernel, a delta-rule memory, routed experts), at equal width and depth on random
+    weights: prefill of 4 x 1024 tokens and decode of 32 sequences at context 1024, measured as --noganex-compare measures its pair, with
+    the achieved FLOP/s or bytes/s of the kernels that carry a step against the measured peaks."""
+    import torch
+    import tgis_b200  # noqa: F401
+    from tgis_b200 import _lib as _libmod
+    from tgis_b200.models.custom_modeling import nasozen_modeling
+    from tgis_b200.utils.synthetic import nasozen_config
+
+    pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        pk = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    PB, PL, DB, DL = 4, 1024, 32, 1024
+    K, Wm = max(args.steps // 4, 4), args.warmup
+    ctx = DL + Wm + K + 2
+    lib = _libmod.load_seq()
+    results = []
+
+    def timed(fn, n):
+        total = 0.0
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / n
+
+    def common(name, raw, r, kernels, extra):
+        out = {"model": name, "dtype": "bf16", "layers": len(raw["layers"]), "prefill_tokens_per_s": PB * PL / (r["pre_ms"] * 1e-3),
+               "decode_tokens_per_s": DB / (r["dec_ms"] * 1e-3), "prefill_ms": r["pre_ms"], "decode_ms_per_step": r["dec_ms"],
+               "decode_graph_tokens_per_s": DB / (r["graph_ms"] * 1e-3), "decode_graph_ms_per_step": r["graph_ms"],
+               "prefill_ms_by_op": {k: round(v, 4) for k, v in r["pre_ops"].items()},
+               "decode_ms_by_op": {k: round(v, 4) for k, v in r["dec_ops"].items()},
+               "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(r["dec_k"].items(), key=lambda kv: -kv[1])},
+               "decode_graph_traced_us": r["dec_total"], "kernels": kernels}
+        out.update(extra)
+        return out
+
+    def us(dec_k, *prefixes):
+        return sum(v for k, v in dec_k.items() if k.startswith(prefixes))
+
+    env = dict(PB=PB, PL=PL, DB=DB, DL=DL, K=K, Wm=Wm, ctx=ctx, timed=timed, lib=lib, hbm=hbm, tens=tens, common=common, us=us)
+    widths = (2048, 4096) if not args.layers else (2048,)
+    for width in widths:
+        raw = nasozen_config(f"nasozen-w{width}")
+        names = ["linear", "embed_scale", "streams_step", "causal_conv", "qk_rot_prepare", "talk_attn", "heads_turn_gate", "mingru_scan", "mlstm_scan",
+                 "gdelta_scan", "group_rmsnorm_gate", "ff_act", "moe_route", "moe_gather_rows", "moe_linear", "ff_gate", "moe_combine_add"]
+        cfg = nasozen_modeling.NasozenConfig(raw)
+        r = _stream_family_measure(raw, cfg, names, PB, PL, DB, DL, K, Wm, timed, lib)
+        shapes = nasozen_modeling.tensor_shapes(raw)
+        par = [l["mixer"] for l in raw["layers"] if l["type"] == "parallel"]
+        attn = [m["left"] for m in par]
+        delta = [l["mixer"] for l in raw["layers"] if l["type"] == "general_delta"]
+        mem = [l["mixer"] for l in raw["layers"] if l["type"] == "mlstm"]
+        S, T = cfg.streams or 1, PB * PL
+        subs = sum(2 if l["mlp"] else 1 for l in raw["layers"])
+        attn_flops = sum(PB * (PL * (PL + 1) // 2) * m["heads"] * (m["dim"] + m["vdim"]) * 2 for m in attn)
+        attn_row = sum(m["kv_heads"] * (m["dim"] + m["vdim"]) for m in attn)       # elements a decoding token reads per cached token
+        delta_b = sum(m["heads"] * m["dim"] * m["dim"] * 4 * 2 for m in delta)     # state read + written per sequence and step
+        mem_b = sum(m["heads"] * m["dim"] * m["vdim"] * 4 * 2 for m in mem)
+        gru_b = sum(m["right"]["width"] * (4 * 2 + 3 * 4 + 2) for m in par)         # state in and out, three fp32 inputs, one typed result
+        # streams in and out once per sublayer, the sublayer's result in, the typed copy out (+ the first launch: embedding row in)
+        stream_b = subs * width * (S * 4 * 2 + 4 + 2) + width * (4 + 2 + S * 4)
+        moes = [l["mlp"] for l in raw["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe"]
+        expert_w = 3 * width * moes[0]["expert"]["ff"]
+        top = moes[0]["router"]["top"]
+        dense_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1] if ".mlp.e" not in n and n != "embed")
+        head_w = shapes["embed"][0] * shapes["embed"][1]
+        lin_flops = 2 * T * (dense_w + len(moes) * top * expert_w) + 2 * PB * head_w
+        dk = r["dec_k"]
+        a_us, m_us, g_us = us(dk, "talk_attn"), dk.get("moe_linear_mma_kernel", 0.0), dk.get("gemm_f16_kernel", 0.0)
+        kernels = {
+            "talk_attn prefill": {"ms": r["pre_ops"]["talk_attn"], "tflops": attn_flops / r["pre_ops"]["talk_attn"] / 1e9,
+                                  "of_measured_tensor": attn_flops / (r["pre_ops"]["talk_attn"] * 1e-3) / tens},
+            "talk_attn decode": {"us": a_us, "of_measured_hbm": DB * ctx * attn_row * 2 / (max(a_us, 1e-9) * 1e-6) / hbm},
+            "gdelta_scan prefill": {"ms": r["pre_ops"]["gdelta_scan"], "tokens_per_s_per_layer": T * len(delta) / (r["pre_ops"]["gdelta_scan"] * 1e-3)},
+            "gdelta_scan decode": {"us": us(dk, "gdelta_scan"), "of_measured_hbm": DB * delta_b / (max(us(dk, "gdelta_scan"), 1e-9) * 1e-6) / hbm},
+            "mlstm_scan prefill": {"ms": r["pre_ops"]["mlstm_scan"], "tokens_per_s_per_layer": T * len(mem) / (r["pre_ops"]["mlstm_scan"] * 1e-3)},
+            "mlstm_scan decode": {"us": us(dk, "mlstm_scan"), "of_measured_hbm": DB * mem_b / (max(us(dk, "mlstm_scan"), 1e-9) * 1e-6) / hbm},
+            "mingru_scan prefill": {"ms": r["pre_ops"]["mingru_scan"], "tokens_per_s_per_layer": T * len(par) / (r["pre_ops"]["mingru_scan"] * 1e-3),
+                                    "of_measured_hbm": T * sum(m["right"]["width"] for m in par) * 14 / (r["pre_ops"]["mingru_scan"] * 1e-3) / hbm},
+            "mingru_scan decode": {"us": us(dk, "mingru_scan"), "of_measured_hbm": DB * gru_b / (max(us(dk, "mingru_scan"), 1e-9) * 1e-6) / hbm},
+            "streams_step prefill": {"ms": r["pre_ops"]["streams_step"], "of_measured_hbm": T * stream_b / (r["pre_ops"]["streams_step"] * 1e-3) / hbm},
+            "streams_step decode": {"us": us(dk, "streams_step"), "launches": subs + 1,
+                                    "of_measured_hbm": DB * stream_b / (max(us(dk, "streams_step"), 1e-9) * 1e-6) / hbm},
+            "linear prefill (projections, one product per expert)": {"ms": r["pre_ops"]["linear"],
+                                                                     "of_measured_tensor": lin_flops / (r["pre_ops"]["linear"] * 1e-3) / tens},
+            "moe_linear decode (grouped, picked experts' weights once)": {"us": m_us, "experts_picked_all_layers": r["picked"], "of_measured_hbm":
+                                                                          r["picked"] * expert_w * 2 / (max(m_us, 1e-9) * 1e-6) / hbm},
+            "linear decode (tcgen05 projections)": {"us": g_us, "of_measured_hbm": (dense_w + head_w) * 2 / (max(g_us, 1e-9) * 1e-6) / hbm},
+        }
+        results.append(common(f"nasozen-w{width}", raw, r, kernels, {"experts": moes[0]["router"]["experts"], "top": top, "streams": S}))
+        results.append(_noganex_side(width, env))
+    print(json.dumps({"metric": "nasozen_compare", "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": Wm, "data": "synthetic",
+                      "config": {"prefill": [PB, PL], "decode": [DB, DL], "l2": "flushed between timed calls"},
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk.get("source")}, "models": results}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1281,6 +1400,8 @@ def main():
                     help="Dubesun beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     ap.add_argument("--noganex-compare", action="store_true",
                     help="Noganex beside Dubesun at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
+    ap.add_argument("--nasozen-compare", action="store_true",
+                    help="Nasozen beside Noganex at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -1290,6 +1411,8 @@ def main():
         return run_dubesun_compare(args)
     if args.noganex_compare:
         return run_noganex_compare(args)
+    if args.nasozen_compare:
+        return run_nasozen_compare(args)
     workload = args.workload or DEFAULT_WORKLOAD
     if workload in MIXED_WORKLOADS:
         if args.impl == "reference":

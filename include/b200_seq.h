@@ -172,7 +172,7 @@ int b200_seq_gdelta_scan(const float* raw, int64_t ldr, int col_r, int col_k, in
  * candidate = x + 1/2 (x >= 0) or sigmoid(x), S <- (1 - z) S + z candidate; out (type out_dt) = S * SiLU(proj[col_g + c]) (col_g < 0: S), times out_scale */
 int b200_seq_mingru_scan(const float* proj, int64_t ld, int col_z, int col_x, int col_g, const void* z_bias, const void* x_bias, int dt,
                          float* state, const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, void* out, int out_dt,
-                         int64_t ld_out, float out_scale, int B, int C, void* stream);
+                         int64_t ld_out, float out_scale, int64_t T, int B, int C, void* stream);
 
 #ifdef __cplusplus
 }

@@ -166,7 +166,7 @@ SEQ_SIGNATURES = {
     "b200_seq_ff_act": (_I, [_P, _I, _L, _P, _I, _L, _L, _I, _P]),
     "b200_seq_heads_turn_gate": (_I, [_P, _P, _L, _P, _P, _I, _I, _P, _P, _I, _L, _F, _L, _I, _I, _P]),
     "b200_seq_gdelta_scan": (_I, [_P, _L, _I, _I, _I, _I, _P, _L, _I, _P, _P, _I, _F, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),
-    "b200_seq_mingru_scan": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _I, _L, _F, _I, _I, _P]),
+    "b200_seq_mingru_scan": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _I, _L, _F, _L, _I, _I, _P]),
     "b200_seq_talk_attn_splits": (_I, [_I, _L, _I, _I, _I, _I, _I, ctypes.POINTER(c_int64)]),
 }
 _SEQ_SHARED = ("b200_last_error", "b200_cuda_peek_error", "b200_launch_count", "b200_kv_alloc_create", "b200_kv_alloc_destroy",

@@ -221,14 +221,38 @@ __global__ void ff_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, in
 // row of u waits in shared memory between the two passes; S <= kMaxStreams.
 constexpr int kMaxStreams = 8;
 
-template <typename T>
+// VEC consecutive fp32 values in one access (VEC 4: 16 bytes, the pointer 16-byte aligned)
+template <int VEC>
+__device__ __forceinline__ void ld_vec(const float* p, float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = p[k];
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void st_vec(T* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4 && sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) stf(p + k, v[k]);
+  }
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(kRowThreads) streams_step_kernel(float* __restrict__ X, int S, const float* __restrict__ init,
                                                                    const float* __restrict__ y, const float* __restrict__ mix,
                                                                    const float* __restrict__ out_coef, const float* __restrict__ in_coef,
                                                                    const T* __restrict__ w, T* __restrict__ typed, int W, float eps) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
   __shared__ float cm[kMaxStreams * kMaxStreams], co[kMaxStreams], ci[kMaxStreams];
   if (threadIdx.x < S * S) cm[threadIdx.x] = mix ? mix[threadIdx.x] : 0.f;
@@ -240,45 +264,60 @@ __global__ void __launch_bounds__(kRowThreads) streams_step_kernel(float* __rest
   const int64_t t = blockIdx.x;
   float* xr = X + t * S * W;
   float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += kRowThreads) {
-    float x[kMaxStreams];
+  for (int i = threadIdx.x * VEC; i < W; i += kRowThreads * VEC) {
+    float x[kMaxStreams][VEC];
 #pragma unroll
     for (int s = 0; s < kMaxStreams; ++s)
-      if (s < S) x[s] = init ? init[t * W + i] : xr[(int64_t)s * W + i];
-    if (y) {
-      const float yv = y[t * W + i];
-      float nx[kMaxStreams];
+      if (s < S) ld_vec<VEC>(init ? init + t * W + i : xr + (int64_t)s * W + i, x[s]);
+    float u[VEC];   // the read of the new streams, gathered while they are written
 #pragma unroll
-      for (int u = 0; u < kMaxStreams; ++u) {
-        if (u >= S) break;
-        float a = co[u] * yv;
+    for (int k = 0; k < VEC; ++k) u[k] = 0.f;
+    if (y) {
+      float yv[VEC];
+      ld_vec<VEC>(y + t * W + i, yv);
+#pragma unroll
+      for (int o = 0; o < kMaxStreams; ++o) {
+        if (o >= S) break;
+        float nx[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) nx[k] = co[o] * yv[k];
 #pragma unroll
         for (int s = 0; s < kMaxStreams; ++s)
-          if (s < S) a = fmaf(cm[s * S + u], x[s], a);
-        nx[u] = a;
+          if (s < S) {
+            const float c = cm[s * S + o];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) nx[k] = fmaf(c, x[s][k], nx[k]);
+          }
+        st_vec<float, VEC>(xr + (int64_t)o * W + i, nx);   // every old stream of this column is in registers already
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) u[k] = fmaf(ci[o], nx[k], u[k]);
       }
+    } else {
 #pragma unroll
       for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) x[s] = nx[s];
-    }
-    if (y || init) {
+        if (s < S) {
+          if (init) st_vec<float, VEC>(xr + (int64_t)s * W + i, x[s]);
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) xr[(int64_t)s * W + i] = x[s];
+          for (int k = 0; k < VEC; ++k) u[k] = fmaf(ci[s], x[s][k], u[k]);
+        }
     }
     if (in_coef) {
-      float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) u = fmaf(ci[s], x[s], u);
-      row[i] = u;
-      q += u * u;
+      for (int k = 0; k < VEC; ++k) q += u[k] * u[k];
+      st_vec<float, VEC>(row + i, u);
     }
   }
   if (!in_coef) return;
   const float rstd = w ? 1.f / sqrtf(block_sum(q, red) / W + eps) : 1.f;
-  if (!w) __syncthreads();
-  for (int i = threadIdx.x; i < W; i += kRowThreads) stf(typed + t * W + i, w ? row[i] * rstd * ldf(w + i) : row[i]);
+  for (int i = threadIdx.x * VEC; i < W; i += kRowThreads * VEC) {   // every thread reads back what it wrote itself
+    float u[VEC];
+    ld_vec<VEC>(row + i, u);
+    if (w) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) u[k] = u[k] * rstd * ldf(w + i + k);
+    }
+    st_vec<T, VEC>(typed + t * W + i, u);
+  }
 }
 
 // out = act(in) element by element over rows of F columns (in may be a column slice: leading dimension ld_in);
@@ -484,15 +523,18 @@ extern "C" int b200_seq_streams_step(float* X, int S, const float* init, const f
     b200_set_last_error("seq_streams_step: 1 <= streams <= 8; a write needs mix and out_coef, a read needs an output");
     return B200_ERR_ARG;
   }
-#define SST(E)                                                                                                                        \
-  do {                                                                                                                                \
-    static bool cfg = false;                                                                                                          \
-    if (!cfg) { cudaFuncSetAttribute(streams_step_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }  \
-    B200_LAUNCH((streams_step_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), (size_t)W * 4, (cudaStream_t)stream, X, S, init, y, mix, \
-                out_coef, in_coef, (const E*)w, (E*)typed, (int)W, eps);                                                              \
+#define SST(E, V)                                                                                                                        \
+  do {                                                                                                                                   \
+    static bool cfg = false;                                                                                                             \
+    if (!cfg) { cudaFuncSetAttribute(streams_step_kernel<E, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }  \
+    B200_LAUNCH((streams_step_kernel<E, V>), dim3((unsigned)T), dim3(kRowThreads), (size_t)W * 4, (cudaStream_t)stream, X, S, init, y, mix, \
+                out_coef, in_coef, (const E*)w, (E*)typed, (int)W, eps);                                                                 \
   } while (0)
-  if (dt == B200_DT_F32) SST(float);
-  else if (dt == B200_DT_BF16) SST(__nv_bfloat16);
+  // 16-byte accesses when every row starts on a 16-byte boundary
+  const bool vec = W % 4 == 0 && ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(init) | reinterpret_cast<uintptr_t>(y) |
+                                   reinterpret_cast<uintptr_t>(typed)) & 15) == 0;
+  if (dt == B200_DT_F32) { if (vec) SST(float, 4); else SST(float, 1); }
+  else if (dt == B200_DT_BF16) { if (vec) SST(__nv_bfloat16, 4); else SST(__nv_bfloat16, 1); }
   else { b200_set_last_error("unknown element type"); return B200_ERR_ARG; }
 #undef SST
   b200_count_launches(1);

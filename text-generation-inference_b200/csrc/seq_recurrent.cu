@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(
 // w = exp(-decay_scale * sigmoid(dlogit + w0)) and a = sigmoid(alogit + a_bias) per head and key channel.
 // raw: rows holding r, k (H x dk each), v (H x dv) and the removal logits (H x dk); dec: rows holding the decay logits (H x dk).
 template <typename TP, int KMAX>
-__global__ void __launch_bounds__(kScanThreads) gdelta_scan_kernel(
+__global__ void __launch_bounds__(kScanThreads, KMAX <= 16 ? 3 : 1) gdelta_scan_kernel(
     const float* __restrict__ raw, int64_t ldr, int col_r, int col_k, int col_v, int col_a, const float* __restrict__ dec, int64_t ldd, int col_d,
     const TP* __restrict__ a_bias, const TP* __restrict__ w0, float decay_scale, float* __restrict__ S_state, const int32_t* __restrict__ state_slots,
     const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ y, int64_t ld_y, int H, int dk, int dv) {
@@ -471,6 +471,56 @@ __global__ void __launch_bounds__(kGruThreads) mingru_scan_kernel(const float* _
     stf(out + (int64_t)t * ld_out + c, (col_g >= 0 ? S * silu_f(row[col_g + c]) : S) * out_scale);
   }
   *sp = S;
+}
+
+// The same recurrence for steps that bring many rows per sequence.  S_t = a_t S_(t-1) + b_t is linear in S, so a sequence's rows are
+// dealt out in NSEG consecutive runs: a block owns (sequence, 32 channels), warp j walks run j from a zero state and leaves the run's
+// product of a_t and its end state; after one barrier every warp folds the runs before its own into its true start state and walks
+// its run again, writing the results.  Chains are NSEG times shorter than in the one-thread-per-channel form; the results differ
+// from it by fp32 rounding only.
+template <typename TP, typename TO, int NSEG>
+__global__ void __launch_bounds__(32 * NSEG) mingru_scan_runs_kernel(const float* __restrict__ proj, int64_t ld, int col_z, int col_x, int col_g,
+                                                                     const TP* __restrict__ z_bias, const TP* __restrict__ x_bias,
+                                                                     float* __restrict__ state, const int32_t* __restrict__ state_slots,
+                                                                     const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids,
+                                                                     TO* __restrict__ out, int64_t ld_out, float out_scale, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float As[NSEG][32], Bs[NSEG][32];
+  const int b = blockIdx.x, lane = threadIdx.x & 31, seg = threadIdx.x >> 5, c = blockIdx.y * 32 + lane;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (t_begin >= t_end) return;   // block-uniform
+  const bool live = c < C;
+  const int per = (t_end - t_begin + NSEG - 1) / NSEG;
+  const int t0 = min(t_begin + seg * per, t_end), t1 = min(t0 + per, t_end);
+  const float zb = (live && z_bias) ? ldf(z_bias + c) : 0.f, xb = (live && x_bias) ? ldf(x_bias + c) : 0.f;
+  float A = 1.f, S = 0.f;
+  if (live) {
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+      const float* row = proj + (int64_t)t * ld;
+      const float z = sigmoid_f(row[col_z + c] + zb), x = row[col_x + c] + xb;
+      const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
+      A *= 1.f - z;
+      S = fmaf(z, cand - S, S);
+    }
+  }
+  As[seg][lane] = A;
+  Bs[seg][lane] = S;
+  __syncthreads();
+  if (!live) return;
+  float* sp = state + (int64_t)state_slots[b] * C + c;
+  S = position_ids[t_begin] == 0 ? 0.f : *sp;
+  for (int j = 0; j < seg; ++j) S = fmaf(As[j][lane], S, Bs[j][lane]);
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t) {
+    const float* row = proj + (int64_t)t * ld;
+    const float z = sigmoid_f(row[col_z + c] + zb), x = row[col_x + c] + xb;
+    const float cand = x >= 0.f ? x + 0.5f : sigmoid_f(x);
+    S = fmaf(z, cand - S, S);
+    stf(out + (int64_t)t * ld_out + c, (col_g >= 0 ? S * silu_f(row[col_g + c]) : S) * out_scale);
+  }
+  if (seg == NSEG - 1) *sp = S;   // the last run ends the sequence's rows (an empty run passes its start state on)
 }
 
 constexpr int kMaxTaps = 8;
@@ -695,13 +745,26 @@ extern "C" int b200_seq_gdelta_scan(const float* raw, int64_t ldr, int col_r, in
 
 // proj fp32 [T, ld]: update-gate logits, candidate inputs and output-gate logits (C columns each) at col_z / col_x / col_g (col_g < 0:
 // no output gate); z_bias, x_bias [C] of element type dt (may be NULL); state fp32 [slots, C] advanced in place -> out [T, ld_out] of
-// type out_dt, times out_scale
+// type out_dt, times out_scale.  T: token rows of the step (steps with many rows per sequence take the kernel that walks runs of rows)
 extern "C" int b200_seq_mingru_scan(const float* proj, int64_t ld, int col_z, int col_x, int col_g, const void* z_bias, const void* x_bias, int dt,
                                     float* state, const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, void* out,
-                                    int out_dt, int64_t ld_out, float out_scale, int B, int C, void* stream) {
+                                    int out_dt, int64_t ld_out, float out_scale, int64_t T, int B, int C, void* stream) {
   if (B == 0 || C == 0) return B200_OK;
-  dim3 grid((unsigned)B, (unsigned)((C + kGruThreads - 1) / kGruThreads));
   cudaStream_t st = (cudaStream_t)stream;
+  if (T >= 8 * (int64_t)B) {   // prompts and portions: a sequence's rows in 16 runs per block of 32 channels
+    constexpr int kRuns = 16;
+    dim3 grid_r((unsigned)B, (unsigned)((C + 31) / 32));
+#define MGR(TO)                                                                                                                              \
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((mingru_scan_runs_kernel<E, TO, kRuns>), grid_r, dim3(32 * kRuns), 0, st, proj, ld, col_z, col_x, col_g, \
+                                       (const E*)z_bias, (const E*)x_bias, state, state_slots, cu_q, position_ids, (TO*)out, ld_out, out_scale, C))
+    if (out_dt == B200_DT_F32) MGR(float);
+    else if (out_dt == B200_DT_BF16) MGR(__nv_bfloat16);
+    else { b200_set_last_error("unknown element type"); return B200_ERR_ARG; }
+#undef MGR
+    b200_count_launches(1);
+    return B200_OK;
+  }
+  dim3 grid((unsigned)B, (unsigned)((C + kGruThreads - 1) / kGruThreads));
 #define MG(TO)                                                                                                                          \
   B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((mingru_scan_kernel<E, TO>), grid, dim3(kGruThreads), 0, st, proj, ld, col_z, col_x, col_g,      \
                                        (const E*)z_bias, (const E*)x_bias, state, state_slots, cu_q, position_ids, (TO*)out, ld_out, out_scale, C))

@@ -596,6 +596,6 @@ def mingru_scan(proj: torch.Tensor, col_z: int, col_x: int, col_g: int, z_bias: 
     assert out.dtype == out_dtype and out.shape == (step.T, width) and out.stride(1) == 1
     _lib.check_seq(_lib.load_seq().b200_seq_mingru_scan(
         _ptr(proj), proj.stride(0), col_z, col_x, col_g, _ptr(z_bias), _ptr(x_bias), 1 if b is None else _dt(b), _ptr(state),
-        _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(out), _dt(out), out.stride(0), float(out_scale), step.B, width, _stream()),
+        _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(out), _dt(out), out.stride(0), float(out_scale), step.T, step.B, width, _stream()),
         "seq_mingru_scan")
     return out

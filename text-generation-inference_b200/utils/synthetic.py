@@ -81,15 +81,35 @@ def noganex_config(name: str) -> dict:
     return {"architecture": "Noganex", "layers": layers, "logit_scale": 1.0, "norm": {"eps": 1e-5}, "vocab": 32000, "width": W}
 
 
+def nasozen_config(name: str) -> dict:
+    """Three layers on three residual streams at the widths of the `noganex-w*` partners: attention (window 2048, half of each head
+    rotated, a sink and a gate per head, four taps) beside a minimal gated recurrent unit of the model's width with a tanh-GELU MLP,
+    the generalised delta rule with 16 routed experts (2 per token), and the matrix memory with routed experts: raw config.json of
+    the Nasozen family."""
+    W = {"nasozen-w2048": 2048, "nasozen-w4096": 4096}[name]
+    moe = {"kind": "moe", "expert": {"ff": W * 11 // 16}, "router": {"experts": 16, "top": 2}}
+    left = {"conv": 4, "dim": 128, "heads": W // 128, "kv_heads": W // 512, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 2048},
+            "rot": {"base": 1000000.0, "dims": 64}}
+    layers = [
+        {"type": "parallel", "mixer": {"left": left, "left_scale": 0.7, "right": {"width": W}, "right_scale": 0.7},
+         "mlp": {"kind": "dense", "ff": W * 4}},
+        {"type": "general_delta", "mixer": {"dim": 128, "heads": W // 128}, "mlp": dict(moe)},
+        {"type": "mlstm", "mixer": {"dim": 128, "gate_cap": 15.0, "heads": W // 128, "vdim": 128}, "mlp": dict(moe)},
+    ]
+    return {"architecture": "Nasozen", "layers": layers, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "streams": 3, "vocab": 32000, "width": W}
+
+
 class SyntheticHybridWeights:
-    """Seeded random tensors of a Fetotar, Dubesun or Noganex configuration, generated on the device by name (the `get_tensor` side
-    of `Weights`)."""
+    """Seeded random tensors of a Fetotar, Dubesun, Noganex or Nasozen configuration, generated on the device by name (the `get_tensor`
+    side of `Weights`)."""
 
     def __init__(self, raw_config: dict, device, dtype, process_group, seed: int = 1234):
         if raw_config.get("architecture") == "Dubesun":
             from ..models.custom_modeling.dubesun_modeling import tensor_shapes
         elif raw_config.get("architecture") == "Noganex":
             from ..models.custom_modeling.noganex_modeling import tensor_shapes
+        elif raw_config.get("architecture") == "Nasozen":
+            from ..models.custom_modeling.nasozen_modeling import tensor_shapes
         else:
             from ..models.custom_modeling.fetotar_modeling import tensor_shapes
         self.shapes, self.device, self.dtype, self.process_group, self.seed = tensor_shapes(raw_config), device, dtype, process_group, seed
@@ -101,6 +121,10 @@ class SyntheticHybridWeights:
         leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
         if leaf == "mix.talk":   # near the identity: every head mostly keeps its own scores
             t = torch.eye(shape[0], device=self.device) + torch.empty(shape, device=self.device).normal_(0.0, 0.1 / shape[0] ** 0.5, generator=gen)
+        elif leaf.startswith("hc"):   # residual streams: mostly kept apart, read as their mean, written alike
+            base = {"mix": torch.eye(shape[0], device=self.device), "in": torch.full(shape, 1.0 / shape[0], device=self.device),
+                    "out": torch.ones(shape, device=self.device)}[leaf.split(".")[-1]]
+            t = base + torch.empty(shape, device=self.device).normal_(0.0, 0.05, generator=gen)
         elif len(shape) == 2:
             std = 0.5 if leaf.endswith("conv") else 1.0 / (shape[1] ** 0.5)
             t = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen)
