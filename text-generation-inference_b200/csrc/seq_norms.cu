@@ -1,6 +1,8 @@
 // Row kernels around an fp32 residual stream: embedding lookup (scaled, or plus a learned position row), layer norm in and out of
 // the stream, RMS norm of the stream with an offset weight, RMS norm of a
-// column slice, grouped RMS norm with a gate, the clamped gated feed-forward activation, and the per-layer token side input.
+// column slice, grouped RMS norm with a gate, the clamped gated feed-forward activation, the per-layer token side input, the step
+// between two sublayers of a decoder with several residual streams (write all streams, read and norm the next input), plain
+// activations, and the turn-back + gate of attention heads whose values carry their position.
 // One block per token row; all statistics and the residual sum in fp32.
 #include "seq_common.cuh"
 

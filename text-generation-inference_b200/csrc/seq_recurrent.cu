@@ -8,6 +8,9 @@
 //   delta_scan_kernel (gated delta rule)  S <- g_t S, u_t = beta_t (v_t - S^T k_t), S <- S + k_t u_t^T, y_t = S^T q_t (the read-out sees the
 //                     token's own write); q_t, k_t unit vectors (x / sqrt(sum x^2 + 1e-6)), q_t times q_scale; beta_t = sigmoid(raw),
 //                     g_t = exp(-exp(A_log) softplus(raw + dt_bias)); q / k shared by the heads of a group.
+//   gdelta_scan_kernel (generalised delta rule)  S <- diag(w_t) S - (a_t * u_t)(u_t^T S) + k_t v_t^T, y_t = S^T r_t with u_t the unit-length
+//                     key, a decay w_t = exp(-c sigmoid(.)) and a removal rate a_t = sigmoid(.) per key channel.
+//   mingru_scan_kernel / mingru_scan_runs_kernel (minimal gated recurrent unit, a state per channel)  S <- (1 - z_t) S + z_t c_t.
 //   causal_conv_silu_kernel / conv_state_update_kernel: short depth-wise causal convolution whose last taps-1 inputs are state.
 //
 // One block owns (sequence, head, 32 value columns) and walks the sequence's tokens of this step in order, whether they are a

@@ -1,6 +1,7 @@
 """Tensor-level wrappers over libb200_seq.so: the kernels of the decoder families with an fp32 stream (latent attention over a paged latent
-cache, differential and distance-biased attention over paged heads, state-space and matrix-memory mixers over fp32 state slots,
-routed feed-forward, the row kernels around the residual stream).
+cache, differential and distance-biased attention over paged heads, head-mixed and sink attention over token-major rows, state-space,
+matrix-memory, delta-rule and gated-unit mixers over fp32 state slots, routed feed-forward, the row kernels around one or several
+residual streams).
 
 Element type `dtype` is torch.bfloat16 or torch.float32 (weights, activations between projections, cache pages); statistics,
 soft-max, recurrences, states and the residual stream are fp32 in both.  CUDA tensors only; there is no eager fallback.

@@ -2,8 +2,10 @@
 family can compose them: latent attention over a paged latent cache (sliding window, rotary part with optional YaRN frequency
 scaling), the selective state-space mixer (Mamba-2 form), the matrix-memory mixer (mLSTM), differential attention (two soft-max
 maps per head, short convolutions after the projections, optionally over another layer's keys and values), attention with a
-learned bias per log-spaced distance bucket, the gated delta rule, attention with head-mixed scores under a chunked mask, and
-the feed-forward layers (clamped gated MLP, gated MLP with biases, routed experts with an optional shared expert).
+learned bias per log-spaced distance bucket, the gated delta rule, attention with head-mixed scores under a chunked mask,
+windowed attention with sink logits, position-carrying values and a gate per head, the minimal gated recurrent unit, two mixers
+side by side on shared products, the generalised delta rule, and the feed-forward layers (clamped gated MLP, gated MLP with
+biases, plain MLP, routed experts with an optional shared expert).
 
 A mixer declares what it keeps per sequence (`cache_spec`): a row of the paged cache per token, or fp32 state tensors in a
 state slot.  `forward(h, step, store)` takes the normed hidden states of a ragged step (ops_seq.RaggedStep: any mix of whole
