@@ -273,6 +273,7 @@ ATTENTION_CASES = [  # heads, kv heads, dim, vdim, rotated columns, window, taps
     (16, 4, 16, 64, 0, 50, 0),     # no rotation (the values stay as projected), no convolution
     (3, 1, 8, 8, 4, 0, 1),         # no window at all, a single tap
     (8, 2, 64, 128, 32, 5, 4),     # a window shorter than a page
+    (16, 16, 64, 256, 32, 50, 2),  # many key heads of wide values: more than one block's shared memory if all groups were staged
 ]
 
 

@@ -16,6 +16,7 @@
 //   talk_attn_kernel      : plain form, any element type and shape.  One block per (query token, slab of 8 heads): raw scores of
 //                           all heads against a tile of 32 keys, the mix, fp32 online soft-max and P V for the slab's heads (a
 //                           warp each).  Prompts, portions and decoded tokens are one case: keys come back from the cache.
+//   group_attn_kernel     : plain form without a mix: one block per (query token, key / value head group, 8 heads of the group).
 //   talk_attn_mma_kernel  : bfloat16 caches, m16n8k16 tensor-core products; see the note above the kernel.
 #include "seq_common.cuh"
 
@@ -169,6 +170,87 @@ __global__ void __launch_bounds__(kTalkWarps * 32) talk_attn_kernel(
         for (int i = 0; i < NV; ++i) {
           const int c = lane + 32 * i;
           if (c < dv) acc[i] = fmaf(pj, vbase[jj * VD + c], acc[i]);
+        }
+      }
+    }
+  }
+  if (own) {
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < dv) out[(t * H + h) * dv + c] = acc[i] * inv;
+    }
+  }
+}
+
+// Plain form without a head mix: no head needs another head's scores, so a block owns (query token, key / value head group, up
+// to 8 query heads of that group) and stages only that group's keys and values - shared memory does not grow with the number of
+// groups.  Same tiles of 32 keys, a warp per head, fp32 online soft-max, window, chunk and sink as above.
+template <typename T, int NV>  // NV = ceil(vdim / 32) value columns per lane
+__global__ void __launch_bounds__(kTalkWarps * 32) group_attn_kernel(
+    const float* __restrict__ q, const T* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
+    int64_t bt_stride, const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H, int G,
+    int d, int dv, int chunk, int window, float scale, int page, const float* __restrict__ sink) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int KP = d + 1, rep = H / G, slabs = (rep + kTalkWarps - 1) / kTalkWarps;
+  float* qs = sm;                          // [8][d], scaled
+  float* kv = qs + kTalkWarps * d;         // keys [32][KP], then values [32][dv]
+  const int64_t t = blockIdx.x;
+  const int g = blockIdx.y / slabs, sub = blockIdx.y % slabs;
+  const int w = warp_id(), lane = lane_id(), nthreads = kTalkWarps * 32;
+  const int hh = sub * kTalkWarps + w;     // head of the group that this warp owns
+  const bool own = hh < rep;
+  const int h = g * rep + (own ? hh : 0);
+  const int b = seq_of_token[t];
+  const int p = (int)position_ids[t];
+  const int j_lo = first_visible(p, chunk, window);
+  for (int idx = threadIdx.x; idx < kTalkWarps * d; idx += nthreads) {
+    const int ww = idx / d, head = sub * kTalkWarps + ww;
+    qs[idx] = head < rep ? q[(t * H + g * rep + head) * d + idx % d] * scale : 0.f;
+  }
+  float m = (sink && own) ? sink[h] : -INFINITY, l = (sink && own) ? 1.f : 0.f, acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) acc[i] = 0.f;
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  const int kcol = k_off + g * d, vcol = v_off + g * dv;
+  for (int j0 = j_lo; j0 <= p; j0 += kTalkKeys) {
+    const int nk = min(kTalkKeys, p - j0 + 1);
+    __syncthreads();  // the previous tile's values are no longer read (first time round: qs is complete after the next barrier)
+    for (int idx = threadIdx.x; idx < nk * d; idx += nthreads) {
+      const int jj = idx / d, c = idx % d, j = j0 + jj;
+      kv[jj * KP + c] = ldf(cache + ((int64_t)table[j / page] * page + j % page) * RW + kcol + c);
+    }
+    __syncthreads();
+    float s = -INFINITY;
+    if (own && lane < nk) {
+      const float* kq = kv + lane * KP;
+      const float* qq = qs + w * d;
+      s = 0.f;
+      for (int i = 0; i < d; ++i) s = fmaf(qq[i], kq[i], s);
+    }
+    __syncthreads();  // keys no longer read
+    for (int idx = threadIdx.x; idx < nk * dv; idx += nthreads) {
+      const int jj = idx / dv, c = idx % dv, j = j0 + jj;
+      kv[idx] = ldf(cache + ((int64_t)table[j / page] * page + j % page) * RW + vcol + c);
+    }
+    __syncthreads();  // values loaded
+    if (own) {
+      const float m_new = fmaxf(m, warp_max(s));
+      const float pr = lane < nk ? expf(s - m_new) : 0.f;
+      const float corr = expf(m - m_new);
+      l = l * corr + warp_sum(pr);
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[i] *= corr;
+      for (int jj = 0; jj < nk; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pr, jj);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < dv) acc[i] = fmaf(pj, kv[jj * dv + c], acc[i]);
         }
       }
     }
@@ -580,6 +662,22 @@ static int launch_talk_plain(const float* q, const void* cache, int64_t RW, int 
   return B200_OK;
 }
 
+template <typename E, int NV>
+static int launch_group_plain(const float* q, const void* cache, int64_t RW, int k_off, int v_off, const int32_t* block_table, int64_t bt_stride,
+                              const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t T, int H, int G, int d, int dv, int chunk,
+                              int window, float scale, int page, const float* sink, cudaStream_t st) {
+  const size_t smem = ((size_t)kTalkWarps * d + (size_t)kTalkKeys * (size_t)max(d + 1, dv)) * 4;
+  if (smem > 200 * 1024) { b200_set_last_error("seq_talk_attn: head size too large for the plain kernel"); return B200_ERR_UNSUPPORTED; }
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(group_attn_kernel<E, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; }
+  const int rep = H / G;
+  dim3 grid((unsigned)T, (unsigned)(G * ((rep + kTalkWarps - 1) / kTalkWarps)));
+  B200_LAUNCH((group_attn_kernel<E, NV>), grid, dim3(kTalkWarps * 32), smem, st, q, (const E*)cache, RW, k_off, v_off, block_table, bt_stride,
+              seq_of_token, position_ids, out, H, G, d, dv, chunk, window, scale, page, sink);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
 // How the tensor-core kernel would run a step: tokens per query tile (0: the shape takes the plain kernel), keys per tile, shared memory
 struct TalkPlan { int QT, KT; size_t smem; };
 
@@ -676,6 +774,16 @@ extern "C" int b200_seq_talk_attn(const float* q, const void* cache, int dt, int
   B200_SEQ_DISPATCH(dt, E, return (launch_talk_plain<E, N>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, position_ids, \
                                                           talk, out, T, H, G, d, dv, chunk, window, scale, page, sink, st)))
   const int nv = (dv + 31) / 32;
+  if (talk == nullptr) {   // no mix: blocks per key / value head group
+#define GRP(N)                                                                                                                                \
+  B200_SEQ_DISPATCH(dt, E, return (launch_group_plain<E, N>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, position_ids, \
+                                                           out, T, H, G, d, dv, chunk, window, scale, page, sink, st)))
+    if (nv <= 1) GRP(1);
+    else if (nv <= 2) GRP(2);
+    else if (nv <= 4) GRP(4);
+    else GRP(8);
+#undef GRP
+  }
   if (nv <= 1) TALK(1);
   else if (nv <= 2) TALK(2);
   else if (nv <= 4) TALK(4);
