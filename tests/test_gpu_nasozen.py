@@ -634,3 +634,48 @@ def test_greedy_generation_through_generate_token(tmp_path):
     assert sure_total >= 12
     mgr = model.kv_cache_manager
     assert mgr.free_blocks == mgr.total_num_gpu_blocks and mgr.free_state_slots == 6
+
+
+def test_sampling_and_logprobs_through_generate_token(tmp_path):
+    """requests that sample (temperature, top-k, a seed) and ask for log-probabilities take the chooser chain on the fp32 logits:
+    the same seed draws the same tokens, ids stay inside the top-k set of the reference's logits, log-probabilities are finite"""
+    import tgis_b200  # noqa: F401
+    from tgis_b200 import pb
+    cfg = orc.random_config(order=("parallel", "general_delta"), loop=(1, 2, 2), mlp=("dense", None), streams=2, window=10)
+    sd = orc.random_state_dict(cfg, seed=17)
+    model = _model(tmp_path, cfg, sd, torch.float32, blocks=32, slots=4)
+    tok, V = model.tokenizer, cfg["vocab"]
+    prompt = _tokens(50, 11, V)
+    text = " ".join(f"<tok{i}>" for i in prompt)
+    n_new, top_k = 5, 4
+
+    def run(batch_id):
+        reqs = [pb.Request(id=i, inputs=text, input_length=len(prompt), truncate=False, max_output_length=n_new,
+                           parameters=pb.NextTokenChooserParameters(temperature=0.9, top_k=top_k, top_p=1.0, seed=1234, min_new_tokens=n_new),
+                           details=pb.RequestedDetails(logprobs=True)) for i in range(2)]
+        out = [[], []]
+        with torch.inference_mode():
+            batch, errs = model.batch_type.from_pb(pb.Batch(id=batch_id, requests=reqs), tok, model.dtype, model.device, None, None, True)
+            assert not errs
+            infos = model.generate_token(batch, first=True)[0]
+            for _ in range(n_new):
+                for t in infos:
+                    out[t.request_id].append((t.token_id, t.logprob))
+                if len(out[0]) == n_new:
+                    break
+                infos = model.generate_token(batch)[0]
+            model.kv_cache_manager.free_sequences(batch.sequence_ids)
+        return out
+
+    first, again = run(0), run(1)
+    assert [t for t, _ in first[0]] == [t for t, _ in again[0]] and [t for t, _ in first[1]] == [t for t, _ in again[1]]
+    assert [t for t, _ in first[0]] == [t for t, _ in first[1]]  # two requests with the same seed and prompt in one batch
+    seq = list(prompt)
+    for t, lp in first[0]:
+        ref = orc.forward(cfg, sd, seq)[-1]
+        ref[2] = float("-inf")
+        assert t in ref.topk(top_k + 1).indices.tolist()
+        assert lp is not None and lp <= 0.0 and lp > -30.0
+        seq.append(t)
+    mgr = model.kv_cache_manager
+    assert mgr.free_blocks == mgr.total_num_gpu_blocks and mgr.free_state_slots == 4
